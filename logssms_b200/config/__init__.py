@@ -1,10 +1,12 @@
 from .base import ConfigError, architecture_of, load_model_config, make_model_config, read_config_json, require
-from .specs import (AttentionSpec, BlockSpec, GatedMLPSpec, Mamba2Spec, MixerSlot, ModelSpec, NormSpec,
-                    RopeSpec, ScheduleEntry)
+from .specs import (AttentionSpec, BlockSpec, DenseMLPSpec, GLASpec, GatedMLPSpec, LatentAttentionSpec, Mamba2Spec, MixerSlot,
+                    ModelSpec, NormSpec, PostNormBlockSpec, RopeSpec, RoutedMLPSpec, ScheduleEntry)
 from .falcon_h1 import FalconH1Config
+from .dudurax import DuduraxConfig
 
 __all__ = [
     "ConfigError", "architecture_of", "load_model_config", "make_model_config", "read_config_json", "require",
     "AttentionSpec", "BlockSpec", "GatedMLPSpec", "Mamba2Spec", "MixerSlot", "ModelSpec", "NormSpec",
-    "RopeSpec", "ScheduleEntry", "FalconH1Config",
+    "RopeSpec", "ScheduleEntry", "FalconH1Config", "DuduraxConfig", "DenseMLPSpec", "GLASpec", "LatentAttentionSpec",
+    "PostNormBlockSpec", "RoutedMLPSpec",
 ]

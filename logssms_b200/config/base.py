@@ -40,6 +40,8 @@ def architecture_of(raw: Mapping[str, Any]) -> str:
     """First entry of `architectures`, as the reference picks it
     (python/logssms/models/register.py:29-38)."""
     archs = raw.get("architectures") or (raw.get("text_config") or {}).get("architectures")
+    if not archs and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]          # a config that names its one architecture as a string
     if not archs:
         raise ConfigError("Model config does not define an architecture")
     return archs[0]

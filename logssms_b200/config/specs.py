@@ -33,6 +33,7 @@ class NormSpec:
     size: int
     eps: float
     kind: str = "rmsnorm"
+    param_name: str = "weight"     # checkpoint name of the weight relative to the norm's prefix ("" : the prefix itself)
 
 
 @dataclass(frozen=True)
@@ -91,6 +92,62 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class GLASpec:
+    """Gated linear attention: a matrix state per head with a decay per key channel,
+    decay = sigmoid(low-rank projection + bias) ** (1 / tau); per-head RMSNorm of the output, SiLU output gate."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    norm_eps: float
+    decay_rank: int | None = None      # None: whatever the checkpoint's low-rank decay projection has
+    kind: str = "gla"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are expanded from one cached latent per token; every head's key has an
+    unrotated part of `nope_dim` (from the latent) and a rotated part of `rot_dim` that all heads share."""
+    hidden_size: int
+    num_heads: int
+    nope_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    softmax_scale: float
+    window: int | None              # None -> all earlier keys
+    position: RopeSpec | None       # rotation of the first `position.rotary_dim` dims of the rotated part
+    norm_eps: float
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """down(act(up(x))), no gate."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "gelu_tanh"
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """Mixture of clamped gated experts with a softmax router, a choice correction, expert groups and identity experts."""
+    hidden_size: int
+    expert_size: int
+    num_experts: int
+    num_identity: int
+    top: int
+    num_groups: int
+    keep_groups: int
+    route_scale: float
+    limit: float
+    act_alpha: float = 1.702
+    kind: str = "routed_mlp"
+
+
+@dataclass(frozen=True)
 class MixerSlot:
     """One mixer of a block: its spec, the checkpoint prefix of its tensors
     (relative to the block's prefix), and the scales applied to the normed
@@ -114,6 +171,22 @@ class BlockSpec:
     feed_forward_norm: NormSpec
     feed_forward_norm_name: str
     kind: str = "prenorm_parallel"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """Post-norm block on a 32-bit stream: x <- norm(skip_scale * x + mixer(x)), then, when it has a feed-forward,
+    x <- norm(skip_scale * x + feed_forward(x))."""
+    prefix: str
+    mixer: MixerSlot
+    mixer_norm: NormSpec
+    mixer_norm_name: str
+    feed_forward: Any                 # None: no feed-forward sublayer (and no second norm)
+    feed_forward_name: str
+    feed_forward_norm: NormSpec | None
+    feed_forward_norm_name: str
+    skip_scale: float = 1.0
+    kind: str = "postnorm"
 
 
 @dataclass(frozen=True)
@@ -143,6 +216,7 @@ class ModelSpec:
     schedule: tuple[ScheduleEntry, ...] = field(default=())
     embedding_kind: str = "embedding"       # registry.EMBEDDINGS: built as cls(vocab_size, hidden_size, multiplier)
     lm_head_kind: str = "lm_head"           # registry.HEADS: built as cls(vocab_size, hidden_size, multiplier, tied_to)
+    embedding_options: tuple[tuple[str, Any], ...] = ()    # further keyword arguments of the embedding's constructor
 
     def resolved_schedule(self) -> tuple[ScheduleEntry, ...]:
         if self.schedule:

@@ -1,0 +1,160 @@
+// Routed feed-forward: the router, the experts' activation, identity experts, and the tanh GELU of dense layers.
+//
+//  moe_route        : 32-bit router per token: logits = W_r h, s = softmax over all n outputs (real and identity
+//                     experts alike); the choice looks at s + correction, restricted to the `keep` groups (of
+//                     n / groups neighbours) whose best member scores highest; the `top` best are chosen; their
+//                     weights are s * scale (no correction, no renormalisation).  Writes the dense weights [T, n]
+//                     (0 where not chosen), the chosen indices and weights [T, top], and per token the summed
+//                     weight of the chosen identity experts (the last n - experts outputs).
+//  moe_activation   : y[t, e, i] = w[t, e] * g~ * sigmoid(act_alpha * g~) * (u~ + 1),  g~ = min(g, limit),
+//                     u~ = clamp(u, -limit, limit), from the packed [gate | up] products of all experts.  The expert's
+//                     weight is applied here, so ONE product with the stacked down matrices sums the experts.
+//  moe_add_identity : out += id_weight[t] * h
+//  gelu_tanh        : 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+#include "lb200/common.cuh"
+using namespace lb200;
+
+constexpr int kRouteMax = 256;        // router outputs
+constexpr int kRouteWarps = 4;        // tokens per CTA
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
+                                 float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_w,
+                                 float* __restrict__ id_weight, int tokens, int width, int n, int experts, int top,
+                                 int groups, int keep, float scale) {
+    __shared__ float zs[kRouteWarps][kRouteMax];
+    __shared__ float cs[kRouteWarps][kRouteMax];
+    __shared__ unsigned char ok[kRouteWarps][kRouteMax];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * kRouteWarps + warp;
+    if (t >= tokens) return;
+    const T* hr = h + (size_t)t * width;
+    float* z = zs[warp];
+    float* c = cs[warp];
+    for (int e = 0; e < n; ++e) {
+        const float* wr = w_router + (size_t)e * width;
+        float a = 0.f;
+        for (int k = lane; k < width; k += 32) a += to_f32(hr[k]) * wr[k];
+        a = warp_sum(a);
+        if (lane == 0) z[e] = a;
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int e = lane; e < n; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n; e += 32) sum += expf(z[e] - mx);
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n; e += 32) {
+        const float s = expf(z[e] - mx) / sum;
+        z[e] = s;
+        c[e] = s + correction[e];
+        ok[warp][e] = 0;
+        dense[(size_t)t * n + e] = 0.f;
+    }
+    __syncwarp();
+    if (lane != 0) return;
+    // the groups that stay: `keep` times the group whose best member is largest (ties: the lower index)
+    const int per = n / groups;
+    for (int r = 0; r < keep; ++r) {
+        int best_g = -1;
+        float best = -INFINITY;
+        for (int g = 0; g < groups; ++g) {
+            if (ok[warp][g * per]) continue;
+            float gm = -INFINITY;
+            for (int i = 0; i < per; ++i) gm = fmaxf(gm, c[g * per + i]);
+            if (best_g < 0 || gm > best) { best = gm; best_g = g; }
+        }
+        if (best_g < 0) break;
+        for (int i = 0; i < per; ++i) ok[warp][best_g * per + i] = 1;
+    }
+    float idw = 0.f;
+    for (int r = 0; r < top; ++r) {
+        int best_e = -1;
+        float best = -INFINITY;
+        for (int e = 0; e < n; ++e)
+            if (ok[warp][e] == 1 && (best_e < 0 || c[e] > best)) { best = c[e]; best_e = e; }
+        if (best_e < 0) { chosen[(size_t)t * top + r] = -1; chosen_w[(size_t)t * top + r] = 0.f; continue; }
+        ok[warp][best_e] = 2;
+        const float wgt = z[best_e] * scale;
+        dense[(size_t)t * n + best_e] = wgt;
+        chosen[(size_t)t * top + r] = best_e;
+        chosen_w[(size_t)t * top + r] = wgt;
+        if (best_e >= experts) idw += wgt;
+    }
+    id_weight[t] = idw;
+}
+
+extern "C" int lb_moe_route(const void* h, const float* w_router, const float* correction, float* dense, int* chosen,
+                            float* chosen_w, float* id_weight, int tokens, int width, int n, int experts, int top, int groups,
+                            int keep, float scale, int dtype, void* stream) {
+    if (tokens <= 0) return kOk;
+    if (n <= 0 || experts < 0 || experts > n || top <= 0 || top > n || groups <= 0 || n % groups || keep <= 0 || keep > groups)
+        return kBadSize;
+    if (n > kRouteMax) return kTooLarge;
+    const int grid = (tokens + kRouteWarps - 1) / kRouteWarps;
+    LB_DISPATCH_DTYPE(dtype, moe_route_kernel<T><<<grid, kRouteWarps * 32, 0, (cudaStream_t)stream>>>(
+        (const T*)h, w_router, correction, dense, chosen, chosen_w, id_weight, tokens, width, n, experts, top, groups, keep, scale));
+    return launch_status();
+}
+
+// gu: [T, experts, 2, ff]; y: [T, experts, ff]; dense: [T, n]
+template <typename T>
+__global__ void moe_activation_kernel(const T* __restrict__ gu, const float* __restrict__ dense, T* __restrict__ y,
+                                      int experts, int ff, int n, float limit, float act_alpha) {
+    const size_t t = blockIdx.z;
+    const int e = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ff) return;
+    const float w = dense[t * n + e];
+    float v = 0.f;
+    if (w != 0.f) {
+        const T* row = gu + (t * experts + e) * 2 * (size_t)ff;
+        const float g = fminf(to_f32(row[i]), limit);
+        const float u = fminf(fmaxf(to_f32(row[ff + i]), -limit), limit);
+        v = w * (g / (1.f + expf(-act_alpha * g)) * (u + 1.f));
+    }
+    y[(t * experts + e) * (size_t)ff + i] = from_f32<T>(v);
+}
+
+extern "C" int lb_moe_activation(const void* gu, const float* dense, void* y, int tokens, int experts, int ff, int n, float limit,
+                                 float act_alpha, int dtype, void* stream) {
+    if (tokens <= 0 || experts <= 0) return kOk;
+    if (ff <= 0 || n < experts || experts > 65535) return kBadSize;
+    dim3 grid((ff + 127) / 128, experts, tokens);
+    LB_DISPATCH_DTYPE(dtype, moe_activation_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        (const T*)gu, dense, (T*)y, experts, ff, n, limit, act_alpha));
+    return launch_status();
+}
+
+template <typename T>
+__global__ void moe_add_identity_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ id_weight, int width) {
+    const size_t t = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const float w = id_weight[t];
+    if (w != 0.f) out[t * width + c] = from_f32<T>(to_f32(out[t * width + c]) + w * to_f32(h[t * width + c]));
+}
+
+extern "C" int lb_moe_add_identity(void* out, const void* h, const float* id_weight, int tokens, int width, int dtype, void* stream) {
+    if (tokens <= 0) return kOk;
+    if (width <= 0) return kBadSize;
+    dim3 grid((width + 255) / 256, tokens);
+    LB_DISPATCH_DTYPE(dtype, moe_add_identity_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)h, id_weight, width));
+    return launch_status();
+}
+
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float z = to_f32(in[i]);
+    out[i] = from_f32<T>(0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+}
+
+extern "C" int lb_gelu_tanh(const void* in, void* out, long n, int dtype, void* stream) {
+    if (n <= 0) return kOk;
+    LB_DISPATCH_DTYPE(dtype, gelu_tanh_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const T*)in, (T*)out, (size_t)n));
+    return launch_status();
+}

@@ -95,6 +95,9 @@ class Engine:
         self._side_stream: torch.cuda.Stream | None = None
         self._aux_streams: list | None = None
         self.steps_run = 0
+        # debugging: a callable (layer run index, x, residual) that sees the stream after every layer run of steps that
+        # run kernel by kernel (`use_graphs=False`)
+        self.layer_tap = None
 
     def _pages_that_fit(self, needs, max_requests: int, memory_ratio: float) -> int:
         """Pages for `memory_ratio` of the device after weights and state slots, capped at what
@@ -268,7 +271,10 @@ class Engine:
             if ctx.num_tokens != ctx.num_requests or device_tokens.numel() != ctx.num_tokens:
                 raise ValueError("device_tokens feeds steps of one token per entry only")
             ctx.token_ids.copy_(device_tokens)
+        if self.layer_tap is not None:
+            ctx.extras["layer_tap"] = self.layer_tap
         x, residual = self.model.forward(ctx)
+        ctx.extras.pop("layer_tap", None)
         self.steps_run += 1
         PROFILER.steps += PROFILER.enabled
         if ctx.logit_rows.numel() == 0:

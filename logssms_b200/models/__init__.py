@@ -33,4 +33,8 @@ from ..config.falcon_h1 import ARCHITECTURE as _FALCON_H1, FalconH1Config  # noq
 
 register_architecture(_FALCON_H1, FalconH1Config)
 
+from ..config.dudurax import ARCHITECTURE as _DUDURAX, DuduraxConfig  # noqa: E402
+
+register_architecture(_DUDURAX, DuduraxConfig)
+
 __all__ = ["Architecture", "DecoderModel", "build_model", "register_architecture"]

@@ -20,7 +20,8 @@ class DecoderModel(Part):
     def __init__(self, spec, perturb_init: bool = False):
         self.spec = spec
         shared: dict = {}
-        self.embedding = EMBEDDINGS.get(spec.embedding_kind)(spec.vocab_size, spec.hidden_size, spec.embedding_multiplier)
+        self.embedding = EMBEDDINGS.get(spec.embedding_kind)(spec.vocab_size, spec.hidden_size, spec.embedding_multiplier,
+                                                             **dict(getattr(spec, "embedding_options", ())))
         self.layers = [BLOCKS.get(b.kind)(b, perturb_init=perturb_init, shared=shared) for b in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, perturb_init)
         self.lm_head = HEADS.get(spec.lm_head_kind)(spec.vocab_size, spec.hidden_size, spec.lm_head_multiplier,
@@ -30,6 +31,11 @@ class DecoderModel(Part):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.layers)}")
         self.num_cache_layers = max(e.cache for e in self.schedule) + 1
+        # an embedding with per-request state (`needs_context`) gets a cache layer of its own behind the blocks'
+        self.embedding_cache_layer = None
+        if getattr(self.embedding, "needs_context", False):
+            self.embedding_cache_layer = self.num_cache_layers
+            self.num_cache_layers += 1
 
     def children(self):
         kids = {self.spec.embedding_name: self.embedding, self.spec.final_norm_name: self.final_norm,
@@ -56,6 +62,8 @@ class DecoderModel(Part):
                 needs[e.cache] = need
             elif needs[e.cache] != need:
                 raise ValueError(f"cache layer {e.cache} is shared by layers with different needs")
+        if self.embedding_cache_layer is not None:
+            needs[self.embedding_cache_layer] = self.embedding.cache_needs()
         return [n if n is not None else CacheNeeds() for n in needs]
 
     def kernel_libraries(self) -> list[str]:
@@ -82,8 +90,12 @@ class DecoderModel(Part):
     def forward(self, ctx):
         """Residual stream after all scheduled layers, as the pair (x, residual) whose sum it is."""
         with nvtx_range("embedding"):
-            x = self.embedding.forward(ctx.token_ids)
+            if self.embedding_cache_layer is not None:
+                x = self.embedding.forward(ctx.token_ids, ctx, self.embedding_cache_layer)
+            else:
+                x = self.embedding.forward(ctx.token_ids)
         residual = None
+        tap = ctx.extras.get("layer_tap")          # debugging: called with (run index, the stream after that layer run)
         for i, e in enumerate(self.schedule):
             # a block may hand its output on already joined with the residual (`SummedRows`) where the norm that
             # comes next takes it: the next block's first norm, which a block names as `input_norm` (a block that
@@ -99,12 +111,19 @@ class DecoderModel(Part):
                     x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
             else:
                 x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
+            if tap is not None:
+                tap(i, x, residual)
         ctx.extras.pop("next_norm_takes_summed", None)
         ctx.extras.pop("next_norm_takes_scaled", None)
         return x, residual
 
     def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the token rows that were asked for."""
+        if isinstance(x, K.StreamRows):          # a 32-bit stream: the wanted rows stay 32-bit up to the norm
+            with nvtx_range("final norm + head"):
+                picked = K.gather_rows(x.f32, rows)
+                (h,), _ = self.final_norm.forward(K.StreamRows(picked, x.act[:0]), None, want_residual=False)
+                return self.lm_head.forward(h)
         x = K.ScaledRows(K.gather_rows(x.rows, rows), x.scale) if isinstance(x, K.ScaledRows) else K.gather_rows(x, rows)
         if residual is not None:
             residual = K.gather_rows(residual, rows)

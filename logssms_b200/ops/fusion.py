@@ -115,3 +115,24 @@ class NormedRows:
             if write:
                 self.shared["written"] = True
         return self._tensor
+
+
+class StreamRows:
+    """A residual stream that is kept in 32-bit whatever the activation dtype: `f32` [rows, width] is the stream, `act`
+    its copy rounded to the activation dtype, which the next sublayer's products read (in a float32 engine both are one
+    tensor).  Post-norm blocks hand these from layer to layer; a norm with `takes_stream_rows = True` normalises them."""
+    __slots__ = ("f32", "act")
+
+    def __init__(self, f32, act):
+        self.f32, self.act = f32, act
+
+    @property
+    def shape(self):
+        return self.act.shape
+
+    @property
+    def dtype(self):
+        return self.act.dtype
+
+    def tensor(self) -> torch.Tensor:
+        return self.act

@@ -1011,3 +1011,231 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act_scale: float) ->
     if GEMM_MODE == "tcgen05" and _tcgen05_ok(x, w_gate_up, None):
         return gemm_tcgen05(x, w_gate_up, swiglu_scale=act_scale)
     return swiglu(linear(x, w_gate_up), act_scale)
+
+
+# --------------------------------------------------------------------------- a 32-bit residual stream (post-norm layers)
+from .fusion import StreamRows      # noqa: E402  (re-exported like the other classes of the protocol)
+
+
+def embed_pair(table: torch.Tensor, pairs: torch.Tensor, ids: torch.Tensor, token_req: torch.Tensor,
+               cu_seqlens: torch.Tensor, start_pos: torch.Tensor, slots: torch.Tensor, prev_state: torch.Tensor,
+               scale: float, buckets: int, mul_prev: int, mul_cur: int, bad_ids: torch.Tensor | None = None) -> StreamRows:
+    """table[id] * scale + pairs[(previous id * mul_prev + id * mul_cur) mod buckets] (row `buckets` for a sequence's
+    first token), summed in 32-bit.  `prev_state`: int32 [slots, 1], the last id each request has fed so far; read
+    for a portion's first token and replaced by the portion's last id."""
+    _cuda(table, pairs, ids, token_req, cu_seqlens, start_pos, slots, prev_state)
+    for t, name in ((ids, "ids"), (token_req, "token_req"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, name)
+    _need(prev_state.dtype == torch.int32 and prev_state.is_contiguous(), "prev_state must be contiguous int32")
+    _need(table.dim() == 2 and table.is_contiguous() and pairs.is_contiguous() and pairs.dtype == table.dtype
+          and pairs.shape == (buckets + 1, table.shape[1]), "pairs table must be [buckets + 1, hidden] of the embedding's dtype")
+    V, H = table.shape
+    T = ids.numel()
+    f32 = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    act = f32 if table.dtype == torch.float32 else torch.empty((T, H), dtype=table.dtype, device=table.device)
+    f = _fn("embed", "lb_embed_pair", [c_void_p] * 10 + [c_int, c_int, c_int, c_int, ctypes.c_longlong, ctypes.c_longlong,
+                                                          c_float, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(f32), None if act is f32 else _ptr(act), _ptr(table), _ptr(pairs), _ptr(ids), _ptr(token_req),
+             _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(prev_state), T, H, V, buckets, mul_prev, mul_cur, scale,
+             _ptr(bad_ids), _code(table), _stream()), "embed_pair")
+    return StreamRows(f32, act)
+
+
+def skip_rmsnorm(stream: StreamRows, y: torch.Tensor | None, skip: float, weight: torch.Tensor, eps: float, *,
+                 extra: torch.Tensor | None = None, row_scale: torch.Tensor | None = None, want_f32: bool = True,
+                 act_dtype: torch.dtype | None = None) -> StreamRows:
+    """RMSNorm(skip * stream + y [+ row_scale[t] * extra]) * weight in 32-bit: the new stream and its copy rounded to
+    the activation dtype (`act_dtype`, default y's).  Without `want_f32` only the rounded copy is made (the norm in
+    front of the output head)."""
+    x = stream.f32
+    _cuda(x, y, weight, extra, row_scale)
+    rows, H = x.shape
+    act_dtype = act_dtype or (y.dtype if y is not None else stream.act.dtype)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.shape == (H,) and weight.is_contiguous(), "norm weight must be float32 [width]")
+    for t, name in ((y, "y"), (extra, "extra")):
+        _need(t is None or (t.shape == x.shape and t.dtype == act_dtype and t.is_contiguous()), f"{name} must match the stream's shape")
+    _need((extra is None) == (row_scale is None), "extra rows come with a scale per row")
+    _need(row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() == rows and row_scale.is_contiguous()),
+          "row_scale must be float32 [rows]")
+    f32 = torch.empty_like(x) if want_f32 else None
+    act = f32 if (act_dtype == torch.float32 and want_f32) else torch.empty((rows, H), dtype=act_dtype, device=x.device)
+    f = _fn("stream_norm", "lb_skip_rmsnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p,
+                                               c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(y), _ptr(extra), _ptr(row_scale), skip, _ptr(weight), eps, _ptr(f32), None if act is f32 else _ptr(act),
+             rows, H, _DTYPE_CODE[act_dtype], _stream()), "skip_rmsnorm", f"(width {H})")
+    return StreamRows(f32, act)
+
+
+# --------------------------------------------------------------------------- gated linear attention
+def gla_scan(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+             slots: torch.Tensor, num_requests: int, num_heads: int, key_dim: int, value_dim: int, tau: float,
+             q_scale: float, request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Token-by-token recurrence S <- diag(sigmoid(z)^(1/tau)) S + k v^T, o = S^T (q * q_scale) per head over every
+    request's tokens.  qkv: [tokens, >= 2*H*key_dim + H*value_dim] with columns q | k | v first (unit column stride);
+    z: float32 [tokens, H*key_dim]; state: float32 [slots, H, key_dim, value_dim], updated in place.  Returns float32
+    [tokens, H*value_dim]."""
+    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, request_list)
+    H, dk, dv = num_heads, key_dim, value_dim
+    T = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= H * (2 * dk + dv), "qkv must hold the columns q | k | v")
+    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
+          "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, name)
+    n = num_requests
+    if request_list is not None:
+        _i32(request_list, "request_list")
+        n = request_list.numel()
+    o = out if out is not None else torch.empty((T, H * dv), dtype=torch.float32, device=qkv.device)
+    item, base = qkv.element_size(), qkv.data_ptr()
+    stride = qkv.stride(0) if T > 1 else qkv.shape[1]
+    f = _fn("gla", "lb_gla_scan", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(base, base + H * dk * item, base + 2 * H * dk * item, stride, _ptr(z), _ptr(o), _ptr(state), _ptr(cu_seqlens),
+             _ptr(start_pos), _ptr(slots), _ptr(request_list), n, H, dk, dv, tau, q_scale, _code(qkv), _stream()),
+           "gla_scan", f"(key_dim {dk}, value_dim {dv})")
+    return o
+
+
+def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, num_heads: int) -> torch.Tensor:
+    """RMSNorm of every head's float32 output with one weight [value_dim] for all heads, times silu(gate); the result
+    has the gate's dtype.  `gate` may be a column view of a wider matrix."""
+    _cuda(o, gate, weight)
+    rows, width = o.shape
+    dv = width // num_heads
+    _need(o.dtype == torch.float32 and o.is_contiguous() and width == num_heads * dv, "o must be contiguous float32 [rows, H*value_dim]")
+    _need(gate.shape == o.shape and gate.stride(1) == 1, "gate must match o, unit column stride")
+    _need(weight.dtype == torch.float32 and weight.shape == (dv,) and weight.is_contiguous(), "weight must be float32 [value_dim]")
+    out = torch.empty((rows, width), dtype=gate.dtype, device=o.device)
+    f = _fn("gla", "lb_gla_norm_gate", [c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(o), _ptr(gate), gate.stride(0) if rows > 1 else gate.shape[1], _ptr(weight), _ptr(out), rows, num_heads, dv,
+             eps, _code(gate), _stream()), "gla_norm_gate")
+    return out
+
+
+# --------------------------------------------------------------------------- attention over a cache of latents
+def latent_prepare(proj: torch.Tensor, num_heads: int, nope_dim: int, rot_dim: int, rank: int, positions: torch.Tensor,
+                   slot_mapping: torch.Tensor, cos_sin: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                   c_cache: torch.Tensor, kr_cache: torch.Tensor, write_cache: bool = True) -> None:
+    """proj: [tokens, H*(nope+rot) + rank + rot] = queries | down-projection.  Stores the normalised latent and the
+    rotated shared key part at `slot_mapping`, and rotates every head's rotated query part in place."""
+    _cuda(proj, positions, slot_mapping, cos_sin, norm_weight, c_cache, kr_cache)
+    T = proj.shape[0]
+    q_cols = num_heads * (nope_dim + rot_dim)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == q_cols + rank + rot_dim, "proj must hold queries | latent | rotated key")
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    _need(cos_sin.dtype == torch.float32 and cos_sin.dim() == 2 and cos_sin.is_contiguous(), "cos/sin table must be contiguous float32")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.shape == (rank,) and norm_weight.is_contiguous(), "latent norm weight must be float32 [rank]")
+    _need(c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.dtype == proj.dtype == kr_cache.dtype
+          and c_cache.shape[-1] == rank and kr_cache.shape[-1] == rot_dim, "latent caches must be [..., rank] and [..., rot_dim] of the activation dtype")
+    f = _fn("attention_latent", "lb_latent_prepare", [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                      c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                                      c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0) if T > 1 else proj.shape[1], q_cols, num_heads, nope_dim, rot_dim, rank, _ptr(positions),
+             _ptr(slot_mapping), _ptr(cos_sin), cos_sin.shape[0], cos_sin.shape[1], _ptr(norm_weight), eps, _ptr(c_cache),
+             _ptr(kr_cache), int(write_cache), T, _code(proj), _stream()), "latent_prepare")
+
+
+def heads_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h, :] = a[t, h, :] @ w[h]  with a [tokens, H, K] (any token and head strides, unit stride in K), w
+    contiguous [H, K, N]; 32-bit accumulation, result in a's dtype."""
+    _cuda(a, w, out)
+    T, H, Kd = a.shape
+    _need(a.stride(2) == 1 and w.is_contiguous() and w.shape[:2] == (H, Kd) and w.dtype == a.dtype, "heads_matmul wants a [T, H, K] and w [H, K, N]")
+    N = w.shape[2]
+    if out is None:
+        out = torch.empty((T, H, N), dtype=a.dtype, device=a.device)
+    _need(out.shape == (T, H, N) and out.stride(2) == 1 and out.dtype == a.dtype, "out must be [T, H, N]")
+    f = _fn("attention_latent", "lb_heads_matmul", [c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int,
+                                                    c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), a.stride(0), a.stride(1), _ptr(w), _ptr(out), out.stride(0), out.stride(1), T, H, Kd, N, _code(a), _stream()),
+           "heads_matmul", f"(K {Kd}, N {N})")
+    return out
+
+
+def latent_attention(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
+                     block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, scale: float,
+                     window: int = 0, token_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Softmax attention in the latent space.  qa: [tokens, H, rank] (queries folded through the key expansion);
+    q_rot: [tokens, H, rot] (a strided view); caches [pages, page_size, rank] and [pages, page_size, rot].  Token t at
+    position p sees keys j of its request with 0 <= p - j < window (0: all).  Returns the weighted sums of the cached
+    latents [tokens, H, rank]; with `token_list` only those rows are written."""
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, token_list)
+    T, H, rank = qa.shape
+    rot = kr_cache.shape[-1]
+    _need(qa.is_contiguous() and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
+          "q_rot must be [tokens, H, rot] with unit stride in its last axis")
+    _need(c_cache.dim() == 3 and c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.shape[2] == rank
+          and c_cache.dtype == qa.dtype == kr_cache.dtype and kr_cache.shape[:2] == c_cache.shape[:2], "latent caches do not fit the queries")
+    _i32(block_table, "block_table")
+    _i32(token_req, "token_req")
+    _i32(positions, "positions")
+    n = T
+    if token_list is not None:
+        _i32(token_list, "token_list")
+        n = token_list.numel()
+    if out is None:
+        out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
+    f = _fn("attention_latent", "lb_latent_attention", [c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
+                                                        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                        c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(qa), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(out), H, rank, rot,
+             c_cache.shape[1], scale, window, _code(qa), _stream()), "latent_attention", f"(rank {rank}, rot {rot})")
+    return out
+
+
+# --------------------------------------------------------------------------- routed feed-forward
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, num_experts: int, top: int, groups: int,
+              keep: int, scale: float):
+    """(dense weights float32 [T, n], chosen int32 [T, top], their weights float32 [T, top], identity weight float32 [T]):
+    see `csrc/moe.cu`.  `w_router` float32 [n, width]; outputs num_experts .. n-1 are identity experts."""
+    _cuda(h, w_router, correction)
+    T, width = h.shape
+    n = w_router.shape[0]
+    _need(h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == width
+          and correction.dtype == torch.float32 and correction.shape == (n,), "router weight float32 [n, width], correction float32 [n]")
+    dense = torch.empty((T, n), dtype=torch.float32, device=h.device)
+    chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    chosen_w = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    idw = torch.empty((T,), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "lb_moe_route", [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(idw), T, width, n,
+             num_experts, top, groups, keep, scale, _code(h), _stream()), "moe_route", f"({n} outputs, top {top}, {groups} groups)")
+    return dense, chosen, chosen_w, idw
+
+
+def moe_activation(gate_up: torch.Tensor, dense: torch.Tensor, num_experts: int, limit: float, act_alpha: float) -> torch.Tensor:
+    """gate_up: [T, experts * 2 * ff] (per expert gate | up); returns [T, experts * ff] with every expert's clamped gated
+    activation times the token's weight for that expert (0 where the expert was not chosen)."""
+    _cuda(gate_up, dense)
+    T = gate_up.shape[0]
+    ff = gate_up.shape[1] // (2 * num_experts)
+    _need(gate_up.is_contiguous() and gate_up.shape[1] == 2 * num_experts * ff, "gate_up must be contiguous [T, experts*2*ff]")
+    _need(dense.dtype == torch.float32 and dense.is_contiguous() and dense.shape[0] == T and dense.shape[1] >= num_experts, "dense weights float32 [T, n]")
+    y = torch.empty((T, num_experts * ff), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("moe", "lb_moe_activation", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(dense), _ptr(y), T, num_experts, ff, dense.shape[1], limit, act_alpha, _code(gate_up), _stream()), "moe_activation")
+    return y
+
+
+def moe_add_identity(out: torch.Tensor, h: torch.Tensor, id_weight: torch.Tensor) -> torch.Tensor:
+    """out += id_weight[t] * h, in place."""
+    _cuda(out, h, id_weight)
+    _need(out.is_contiguous() and h.is_contiguous() and out.shape == h.shape and out.dtype == h.dtype and id_weight.dtype == torch.float32,
+          "moe_add_identity wants matching contiguous rows and float32 weights")
+    f = _fn("moe", "lb_moe_add_identity", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(h), _ptr(id_weight), out.shape[0], out.shape[1], _code(out), _stream()), "moe_add_identity")
+    return out
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    _cuda(x)
+    _need(x.is_contiguous(), "gelu_tanh wants a contiguous tensor")
+    out = torch.empty_like(x)
+    f = _fn("moe", "lb_gelu_tanh", [c_void_p, c_void_p, c_long, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(out), x.numel(), _code(x), _stream()), "gelu_tanh")
+    return out

@@ -5,9 +5,13 @@ from .rope import RotaryEmbedding, inverse_frequencies
 from .attention import Attention
 from .mamba2 import Mamba2
 from .mlp import GatedMLP
-from .embedding import Embedding, LMHead
-from .block import PreNormParallelBlock
+from .gla import GatedLinearAttention
+from .latent_attention import LatentAttention
+from .moe import DenseMLP, RoutedMLP
+from .embedding import BareLMHead, Embedding, LMHead, PairEmbedding
+from .block import PostNormBlock, PreNormParallelBlock
 
 __all__ = ["MATRIX", "TABLE", "VECTOR", "ParamSpec", "Part", "Runtime", "StepContext", "RMSNorm",
            "RotaryEmbedding", "inverse_frequencies", "Attention", "Mamba2", "GatedMLP", "Embedding", "LMHead",
-           "PreNormParallelBlock"]
+           "PreNormParallelBlock", "PostNormBlock", "GatedLinearAttention", "LatentAttention", "DenseMLP", "RoutedMLP",
+           "PairEmbedding", "BareLMHead"]

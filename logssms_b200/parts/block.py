@@ -141,3 +141,62 @@ class PreNormParallelBlock(Part):
             # the norm that reads the output next applies the feed-forward's output multiplier while it loads it
             return self.feed_forward.forward(h, lazy_scale=True), residual
         return self.feed_forward.forward(h), residual
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(Part):
+    """x <- norm1(skip_scale * x + mixer(x)); then, with a feed-forward, x <- norm2(skip_scale * x + ff(x)).
+
+    The stream x is 32-bit whatever the activation dtype (`K.StreamRows`): the sum and the norm are made in 32-bit by
+    one kernel, which also leaves the copy rounded to the activation dtype that the next sublayer's products read.  A
+    block returns (stream, None): nothing is left to be added."""
+    input_norm = None            # no norm reads this block's input: it is handed the stream as it is
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        m = spec.mixer
+        if m.in_scale != 1.0 or m.out_scale != 1.0:
+            raise ValueError("postnorm blocks take a mixer without input or output scales")
+        self.mixer = MIXERS.get(m.spec.kind)(m.spec, perturb_init=perturb_init, shared=shared)
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, perturb_init)
+        self.feed_forward = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init,
+                                                                          shared=shared)
+            self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, perturb_init)
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "post"):
+                raise ValueError("postnorm blocks need norms with a post-norm form (`post`)")
+
+    def children(self):
+        s = self.spec
+        kids = {s.mixer_norm_name: self.mixer_norm, s.mixer.name: self.mixer}
+        if self.feed_forward is not None:
+            kids[s.feed_forward_norm_name] = self.ff_norm
+            kids[s.feed_forward_name] = self.feed_forward
+        return kids
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def setup(self, rt) -> None:
+        self.mixer.setup(rt)
+        if self.feed_forward is not None:
+            self.feed_forward.setup(rt)
+
+    def forward(self, x, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        if not isinstance(x, K.StreamRows) or residual is not None:
+            raise ValueError("a postnorm block takes a 32-bit stream (`StreamRows`), as its embedding or the block before leaves it")
+        skip = self.spec.skip_scale
+        with nvtx_range(self.spec.mixer.spec.kind):
+            y = self.mixer.forward(x.act, ctx, cache_layer, writes_cache)
+        x = self.mixer_norm.post(x, y, skip)
+        if self.feed_forward is not None:
+            with nvtx_range(self.spec.feed_forward.kind):
+                y = self.feed_forward.forward(x.act)
+            if isinstance(y, tuple):          # (rows, rows to add with a weight per row): the norm's kernel adds them
+                y, extra, row_scale = y
+                x = self.ff_norm.post(x, y, skip, extra=extra, row_scale=row_scale)
+            else:
+                x = self.ff_norm.post(x, y, skip)
+        return x, None

@@ -29,11 +29,46 @@ class Embedding(Part):
         return K.embed_gather(self.weight, ids, self.multiplier, self.bad_ids)
 
 
+@EMBEDDINGS.register("pair_embedding")
+class PairEmbedding(Part):
+    """Token embedding times a multiplier plus a hashed embedding of the (previous token, token) pair:
+    row (previous * mul_prev + token * mul_cur) mod buckets of a second table, whose last row (number `buckets`)
+    serves a sequence's first token.  The sum is made in 32-bit and starts a 32-bit stream (`K.StreamRows`).  The
+    previous token is per-request state (one int32 per slot), so that prompts may be cut anywhere and decoded ids
+    that never visit the host are still seen.  Tensors: `embed`, `bigram`."""
+    kernels = ("embed",)
+    needs_context = True      # forward(ids, ctx, cache_layer): the model gives it a cache layer for its state
+
+    def __init__(self, vocab_size: int, hidden_size: int, multiplier: float = 1.0, *, buckets: int, mul_prev: int,
+                 mul_cur: int):
+        self.vocab_size, self.hidden_size, self.multiplier = vocab_size, hidden_size, multiplier
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        self.weight = self.pairs = self.bad_ids = None
+
+    def param_specs(self):
+        return {"embed": ParamSpec((self.vocab_size, self.hidden_size), MATRIX),
+                "bigram": ParamSpec((self.buckets + 1, self.hidden_size), MATRIX)}
+
+    def bind(self, t):
+        self.weight, self.pairs = t["embed"], t["bigram"]
+        self.bad_ids = torch.zeros(1, dtype=torch.int32, device=self.weight.device)
+
+    def cache_needs(self):
+        from ..cache import CacheNeeds, StateNeed
+        return CacheNeeds(states=(StateNeed("previous_token", (1,), torch.int32),))
+
+    def forward(self, ids: torch.Tensor, ctx=None, cache_layer: int | None = None):
+        state = ctx.cache.states[cache_layer]["previous_token"]
+        return K.embed_pair(self.weight, self.pairs, ids, ctx.token_req, ctx.cu_seqlens, ctx.start_pos, ctx.slots, state,
+                            self.multiplier, self.buckets, self.mul_prev, self.mul_cur, self.bad_ids)
+
+
 @HEADS.register("lm_head")
 class LMHead(Part):
     """logits = float32((h W^T) * multiplier); W is the embedding table when the model ties them
     (python/logssms/layers/embedding.py:94-106, python/logssms/models/falcon_h1.py:237)."""
     kernels = ("norm", "linear_skinny", "gemm_tcgen05")
+    param_name = "weight"         # checkpoint name of the matrix relative to the head's prefix
 
     def __init__(self, vocab_size: int, hidden_size: int, multiplier: float, tied_to: Embedding | None):
         self.vocab_size, self.hidden_size, self.multiplier, self.tied_to = vocab_size, hidden_size, multiplier, tied_to
@@ -42,10 +77,10 @@ class LMHead(Part):
     def param_specs(self):
         if self.tied_to is not None:
             return {}
-        return {"weight": ParamSpec((self.vocab_size, self.hidden_size), MATRIX)}
+        return {self.param_name: ParamSpec((self.vocab_size, self.hidden_size), MATRIX)}
 
     def bind(self, t):
-        self._weight = t.get("weight")
+        self._weight = t.get(self.param_name)
 
     @property
     def weight(self) -> torch.Tensor:
@@ -53,3 +88,9 @@ class LMHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return K.linear(h, self.weight, out_scale=self.multiplier, out_f32=True)
+
+
+@HEADS.register("lm_head_bare")
+class BareLMHead(LMHead):
+    """The same head whose matrix is stored under the head's prefix itself (`head`, not `head.weight`)."""
+    param_name = ""

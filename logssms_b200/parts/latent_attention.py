@@ -1,0 +1,79 @@
+"""Attention over a paged cache of latents: one compressed row and one rotated key part per token."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import CacheNeeds, PagedNeed, PagedTensor
+from ..ops import kernels as K
+from ..registry import MIXERS, POSITION_ENCODINGS
+from .base import MATRIX, VECTOR, ParamSpec, Part, ones_init
+from .rope import NoPositionEncoding
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Part):
+    """q = W_q h, per head [nope_dim | rot_dim]; W_dkv h = [latent (kv_rank) | rotated key part (rot_dim)].  The
+    latent is RMS-normed (c), the key part and every head's rot_dim query part are rotated; only c and the key part
+    are cached, per token, in pages.  A head's key is [W_uk,h c | key part], its value W_uv,h c; scores are scaled by
+    `softmax_scale`, position i sees j with 0 <= i - j < window.
+
+    The attention runs in the latent space: the query's unrotated part is folded through W_uk,h once per token, the
+    softmax-weighted sum of the cached c rows is expanded through W_uv,h afterwards, so no key or value is ever
+    expanded and a token costs (kv_rank + rot_dim) numbers of cache.  Tensors: q, dkv, dkv.norm, uk, uv, o."""
+    kernels = ("attention_latent", "rope", "linear_skinny", "gemm_tcgen05")
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        self._jitter = 0.1 if perturb_init else 0.0
+        if spec.position is None:
+            self.position = NoPositionEncoding()
+        else:
+            key = ("position", spec.position)
+            if shared is not None and key in shared:
+                self.position = shared[key]
+            else:
+                self.position = POSITION_ENCODINGS.get(spec.position.kind)(spec.position)
+                if shared is not None:
+                    shared[key] = self.position
+        self.in_w = self.norm_w = self.uk = self.uv_t = self.o_w = None
+
+    def param_specs(self):
+        s = self.spec
+        return {
+            "q": ParamSpec((s.num_heads * (s.nope_dim + s.rot_dim), s.hidden_size), MATRIX),
+            "dkv": ParamSpec((s.kv_rank + s.rot_dim, s.hidden_size), MATRIX),
+            "dkv.norm": ParamSpec((s.kv_rank,), VECTOR, ones_init(self._jitter)),
+            "uk": ParamSpec((s.num_heads * s.nope_dim, s.kv_rank), MATRIX),
+            "uv": ParamSpec((s.num_heads * s.value_dim, s.kv_rank), MATRIX),
+            "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim), MATRIX),
+        }
+
+    def bind(self, t):
+        s = self.spec
+        self.in_w = torch.cat([t["q"], t["dkv"]], 0).contiguous()
+        self.norm_w, self.o_w = t["dkv.norm"], t["o"]
+        self.uk = t["uk"].view(s.num_heads, s.nope_dim, s.kv_rank).contiguous()                       # [H, K = nope, N = rank]
+        self.uv_t = t["uv"].view(s.num_heads, s.value_dim, s.kv_rank).transpose(1, 2).contiguous()     # [H, K = rank, N = value]
+
+    def setup(self, rt) -> None:
+        self.position.setup(rt)
+
+    def cache_needs(self) -> CacheNeeds:
+        s = self.spec
+        return CacheNeeds(kv=PagedNeed((PagedTensor("c", (s.kv_rank,)), PagedTensor("kr", (s.rot_dim,))), s.window))
+
+    def forward(self, x: torch.Tensor, ctx, cache_layer: int, writes_cache: bool = True) -> torch.Tensor:
+        s = self.spec
+        T, H = x.shape[0], s.num_heads
+        gi = ctx.cache.group_of_layer[cache_layer]
+        group = ctx.cache.groups[gi]
+        c_cache, kr_cache = group.tensor("c", cache_layer), group.tensor("kr", cache_layer)
+        proj = K.linear(x, self.in_w)                                      # queries | latent | rotated key part
+        K.latent_prepare(proj, H, s.nope_dim, s.rot_dim, s.kv_rank, ctx.positions, ctx.slot_mappings[gi],
+                         self.position.table, self.norm_w, s.norm_eps, c_cache, kr_cache, writes_cache)
+        q = proj[:, :H * (s.nope_dim + s.rot_dim)].view(T, H, s.nope_dim + s.rot_dim)
+        qa = K.heads_matmul(q[:, :, :s.nope_dim], self.uk)                 # [T, H, rank]
+        lat = K.latent_attention(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
+                                 ctx.positions, s.softmax_scale, s.window or 0)
+        o = K.heads_matmul(lat, self.uv_t)                                 # [T, H, value]
+        return K.linear(o.view(T, H * s.value_dim), self.o_w)

@@ -1,0 +1,86 @@
+"""Feed-forwards without a SwiGLU: the dense up/act/down layer and the routed mixture of clamped gated experts."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels as K
+from ..registry import FEED_FORWARDS
+from .base import MATRIX, VECTOR, ParamSpec, Part, normal_init
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(Part):
+    """down(act(up(x))) with the tanh form of GELU.  Tensors: up, down."""
+    kernels = ("moe", "linear_skinny", "gemm_tcgen05")
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        if spec.activation != "gelu_tanh":
+            raise ValueError(f"dense_mlp knows the activation gelu_tanh, not {spec.activation!r}")
+        self.spec = spec
+        self.up = self.down = None
+
+    def param_specs(self):
+        s = self.spec
+        return {"up": ParamSpec((s.intermediate_size, s.hidden_size), MATRIX),
+                "down": ParamSpec((s.hidden_size, s.intermediate_size), MATRIX)}
+
+    def bind(self, t):
+        self.up, self.down = t["up"], t["down"]
+
+    def setup(self, rt) -> None:
+        pass
+
+    def forward(self, x: torch.Tensor):
+        return K.linear(K.gelu_tanh(K.linear(x, self.up)), self.down)
+
+
+@FEED_FORWARDS.register("routed_mlp")
+class RoutedMLP(Part):
+    """`num_experts` gated experts and `num_identity` identity experts behind one softmax router.
+
+    Router (32-bit): s = softmax(W_r h) over all outputs; the choice is made on s + correction among the experts of
+    the `keep_groups` best of `num_groups` groups of neighbours; the `top` chosen ones weigh in with s * route_scale.
+    Expert: g = min(W_gate h, limit), u = clamp(W_up h, +-limit), y = g sigmoid(act_alpha g) (u + 1), output W_down y.
+    An identity expert's output is h itself.
+
+    All experts' gate and up matrices are one stacked matrix, and so are their down matrices; the activation kernel
+    multiplies every expert's y by the token's weight for that expert (0: not chosen), so the one stacked down product
+    is already the weighted sum over the experts.  `forward` returns (rows, h, identity weight per row): the norm that
+    follows adds weight * h in 32-bit.  Tensors: router, correction, e<i>.gate, e<i>.up, e<i>.down."""
+    kernels = ("moe", "linear_skinny", "gemm_tcgen05")
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        self.router = self.correction = self.gate_up = self.down = None
+
+    def param_specs(self):
+        s = self.spec
+        n = s.num_experts + s.num_identity
+        specs = {"router": ParamSpec((n, s.hidden_size), VECTOR, normal_init(0.5)),
+                 "correction": ParamSpec((n,), VECTOR, normal_init(0.05))}
+        for e in range(s.num_experts):
+            specs[f"e{e}.gate"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX)
+            specs[f"e{e}.up"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX)
+            specs[f"e{e}.down"] = ParamSpec((s.hidden_size, s.expert_size), MATRIX)
+        return specs
+
+    def bind(self, t):
+        s = self.spec
+        self.router, self.correction = t["router"], t["correction"]
+        self.gate_up = torch.cat([t[f"e{e}.{n}"] for e in range(s.num_experts) for n in ("gate", "up")], 0).contiguous()
+        self.down = torch.cat([t[f"e{e}.down"] for e in range(s.num_experts)], 1).contiguous()
+
+    def setup(self, rt) -> None:
+        pass
+
+    def forward(self, x: torch.Tensor):
+        s = self.spec
+        dense, _, _, id_weight = K.moe_route(x, self.router, self.correction, s.num_experts, s.top, s.num_groups,
+                                             s.keep_groups, s.route_scale)
+        if s.num_experts == 0:
+            return torch.zeros_like(x), x, id_weight
+        y = K.moe_activation(K.linear(x, self.gate_up), dense, s.num_experts, s.limit, s.act_alpha)
+        out = K.linear(y, self.down)
+        if s.num_identity == 0:
+            return out
+        return out, x, id_weight

@@ -13,24 +13,39 @@ class RMSNorm(Part):
     """`forward(x, residual, other=..., in_scales=..., out_scales=...)`:
     residual <- (x [scaled, + other scaled]) + residual ; outputs = rmsnorm(residual) * out_scale_k.
     (python/logssms/layers/norm.py:56-97, python/logssms/kernel/norm.py:8-52.)"""
-    kernels = ("norm", "linear_skinny")
     can_defer = True          # forward() takes `defer=`: see there
     takes_summed_rows = True  # forward() takes `K.SummedRows` as x: the product before has joined the residual already
     takes_scaled_rows = True  # forward() takes `K.ScaledRows` as x: it applies the pending multiplier while it loads x
+    takes_stream_rows = True  # forward() takes `K.StreamRows` as x (a 32-bit stream); `post()` is the post-norm form
+    kernels = ("norm", "linear_skinny", "stream_norm")
 
     def __init__(self, spec, perturb_init: bool = False):
         self.size, self.eps = spec.size, spec.eps
+        self.param_name = getattr(spec, "param_name", "weight")
         self._jitter = 0.1 if perturb_init else 0.0
         self.weight: torch.Tensor | None = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.size,), VECTOR, ones_init(self._jitter))}
+        return {self.param_name: ParamSpec((self.size,), VECTOR, ones_init(self._jitter))}
+
+    def bind(self, t):
+        self.weight = t[self.param_name]
+
+    def post(self, stream, y, skip_scale: float = 1.0, *, extra=None, row_scale=None):
+        """Post-norm on a 32-bit stream: norm(skip_scale * stream + y [+ row_scale[t] * extra]) as `K.StreamRows`."""
+        return K.skip_rmsnorm(stream, y, skip_scale, self.weight, self.eps, extra=extra, row_scale=row_scale)
 
     def forward(self, x, residual=None, *, other=None, in_scales=(1.0, 1.0), out_scales=(1.0,), want_residual=True,
                 defer=False):
         """With `defer` (the caller's consumers all take `NormedRows`: their first step is a product), and
         few enough rows, nothing is launched here: the outputs are `NormedRows` that the consumers' products
         normalise in their prologue, and the new residual is a fresh tensor that the first of them writes."""
+        if isinstance(x, K.StreamRows):
+            # a 32-bit stream: normalised in 32-bit, handed on in the activation dtype
+            if residual is not None or other is not None:
+                raise ValueError("a 32-bit stream carries its residual itself")
+            normed = K.skip_rmsnorm(x, None, 1.0, self.weight, self.eps, want_f32=False, act_dtype=x.act.dtype).act
+            return tuple(normed if s == 1.0 else K.scale(normed, s) for s in out_scales), None
         if isinstance(x, K.ScaledRows):
             # the multiplier of the product that made x rides in this norm's load of x (as in_scales[0])
             if other is None and in_scales[0] == 1.0:

@@ -90,8 +90,10 @@ def check_and_place(model: Part, stored: dict[str, torch.Tensor], dtype: torch.d
     unexpected = [n for n in stored if n not in expected
                   and not (n in twins and twins[n] in stored and stored[n].shape == stored[twins[n]].shape
                            and torch.equal(stored[n], stored[twins[n]]))]
+    # (a dimension that a part declares as -1 is whatever the checkpoint has: a size that config.json does not give)
+    fits = lambda got, want: len(got) == len(want) and all(w == -1 or g == w for g, w in zip(got, want))
     wrong = [(n, stored[n].shape, expected[n].shape) for n in expected
-             if n in stored and tuple(stored[n].shape) != tuple(expected[n].shape)]
+             if n in stored and not fits(tuple(stored[n].shape), tuple(expected[n].shape))]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, source)
     return {n: _held(stored[n], spec.role, dtype).to(device).contiguous() for n, spec in expected.items()}
