@@ -5,7 +5,7 @@ import torch
 
 from ..ops import kernels as K
 from ..registry import EMBEDDINGS, HEADS
-from .base import MATRIX, ParamSpec, Part
+from .base import MATRIX, ParamSpec, Part, normal_init
 
 
 @EMBEDDINGS.register("embedding")
@@ -46,8 +46,9 @@ class PairEmbedding(Part):
         self.weight = self.pairs = self.bad_ids = None
 
     def param_specs(self):
-        return {"embed": ParamSpec((self.vocab_size, self.hidden_size), MATRIX),
-                "bigram": ParamSpec((self.buckets + 1, self.hidden_size), MATRIX)}
+        # random weights: both tables of a size that matters in the sum
+        return {"embed": ParamSpec((self.vocab_size, self.hidden_size), MATRIX, normal_init(1.0 / max(abs(self.multiplier), 1e-3))),
+                "bigram": ParamSpec((self.buckets + 1, self.hidden_size), MATRIX, normal_init(0.7))}
 
     def bind(self, t):
         self.weight, self.pairs = t["embed"], t["bigram"]

@@ -30,14 +30,16 @@ class GatedLinearAttention(Part):
         s = self.spec
         qk, vg = s.num_heads * s.key_dim, s.num_heads * s.value_dim
         rank = -1 if s.decay_rank is None else s.decay_rank
+        # random weights: products of unit-size rows stay of unit size; decays from long to short memories
+        fan = normal_init(s.hidden_size ** -0.5)
         return {
-            "q": ParamSpec((qk, s.hidden_size), MATRIX), "k": ParamSpec((qk, s.hidden_size), MATRIX),
-            "v": ParamSpec((vg, s.hidden_size), MATRIX), "g": ParamSpec((vg, s.hidden_size), MATRIX),
-            "o": ParamSpec((s.hidden_size, vg), MATRIX),
+            "q": ParamSpec((qk, s.hidden_size), MATRIX, fan), "k": ParamSpec((qk, s.hidden_size), MATRIX, fan),
+            "v": ParamSpec((vg, s.hidden_size), MATRIX, fan), "g": ParamSpec((vg, s.hidden_size), MATRIX, fan),
+            "o": ParamSpec((s.hidden_size, vg), MATRIX, normal_init(2.0 * vg ** -0.5)),
             "norm": ParamSpec((s.value_dim,), VECTOR, ones_init(self._jitter)),
-            "a1": ParamSpec((rank, s.hidden_size), MATRIX),
-            "a2": ParamSpec((qk, rank), MATRIX, normal_init(0.3)),
-            "a2.b": ParamSpec((qk,), VECTOR, normal_init(1.0)),
+            "a1": ParamSpec((rank, s.hidden_size), MATRIX, fan),
+            "a2": ParamSpec((qk, rank), MATRIX, normal_init(max(rank, 1) ** -0.5)),
+            "a2.b": ParamSpec((qk,), VECTOR, normal_init(3.0)),
         }
 
     def bind(self, t):

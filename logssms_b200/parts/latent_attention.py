@@ -6,7 +6,7 @@ import torch
 from ..cache import CacheNeeds, PagedNeed, PagedTensor
 from ..ops import kernels as K
 from ..registry import MIXERS, POSITION_ENCODINGS
-from .base import MATRIX, VECTOR, ParamSpec, Part, ones_init
+from .base import MATRIX, VECTOR, ParamSpec, Part, normal_init, ones_init
 from .rope import NoPositionEncoding
 
 
@@ -39,13 +39,15 @@ class LatentAttention(Part):
 
     def param_specs(self):
         s = self.spec
+        fan = normal_init(s.hidden_size ** -0.5)          # random weights: products of unit-size rows stay of unit size
+        up = normal_init(s.kv_rank ** -0.5)
         return {
-            "q": ParamSpec((s.num_heads * (s.nope_dim + s.rot_dim), s.hidden_size), MATRIX),
-            "dkv": ParamSpec((s.kv_rank + s.rot_dim, s.hidden_size), MATRIX),
+            "q": ParamSpec((s.num_heads * (s.nope_dim + s.rot_dim), s.hidden_size), MATRIX, fan),
+            "dkv": ParamSpec((s.kv_rank + s.rot_dim, s.hidden_size), MATRIX, fan),
             "dkv.norm": ParamSpec((s.kv_rank,), VECTOR, ones_init(self._jitter)),
-            "uk": ParamSpec((s.num_heads * s.nope_dim, s.kv_rank), MATRIX),
-            "uv": ParamSpec((s.num_heads * s.value_dim, s.kv_rank), MATRIX),
-            "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim), MATRIX),
+            "uk": ParamSpec((s.num_heads * s.nope_dim, s.kv_rank), MATRIX, up),
+            "uv": ParamSpec((s.num_heads * s.value_dim, s.kv_rank), MATRIX, up),
+            "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim), MATRIX, normal_init(2.0 * (s.num_heads * s.value_dim) ** -0.5)),
         }
 
     def bind(self, t):

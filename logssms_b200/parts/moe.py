@@ -21,8 +21,8 @@ class DenseMLP(Part):
 
     def param_specs(self):
         s = self.spec
-        return {"up": ParamSpec((s.intermediate_size, s.hidden_size), MATRIX),
-                "down": ParamSpec((s.hidden_size, s.intermediate_size), MATRIX)}
+        return {"up": ParamSpec((s.intermediate_size, s.hidden_size), MATRIX, normal_init(s.hidden_size ** -0.5)),
+                "down": ParamSpec((s.hidden_size, s.intermediate_size), MATRIX, normal_init(2.0 * s.intermediate_size ** -0.5))}
 
     def bind(self, t):
         self.up, self.down = t["up"], t["down"]
@@ -56,12 +56,13 @@ class RoutedMLP(Part):
     def param_specs(self):
         s = self.spec
         n = s.num_experts + s.num_identity
-        specs = {"router": ParamSpec((n, s.hidden_size), VECTOR, normal_init(0.5)),
+        fan = normal_init(s.hidden_size ** -0.5)          # random weights: products of unit-size rows stay of unit size
+        specs = {"router": ParamSpec((n, s.hidden_size), VECTOR, normal_init(1.5 * s.hidden_size ** -0.5)),
                  "correction": ParamSpec((n,), VECTOR, normal_init(0.05))}
         for e in range(s.num_experts):
-            specs[f"e{e}.gate"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX)
-            specs[f"e{e}.up"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX)
-            specs[f"e{e}.down"] = ParamSpec((s.hidden_size, s.expert_size), MATRIX)
+            specs[f"e{e}.gate"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX, fan)
+            specs[f"e{e}.up"] = ParamSpec((s.expert_size, s.hidden_size), MATRIX, fan)
+            specs[f"e{e}.down"] = ParamSpec((s.hidden_size, s.expert_size), MATRIX, normal_init(3.0 * s.expert_size ** -0.5))
         return specs
 
     def bind(self, t):

@@ -65,9 +65,14 @@ def gla(h, W, state, *, heads, dim, vdim, tau, eps):
 
 
 # --------------------------------------------------------------------------- latent attention with a window
-def rotate_half(x, pos, base):
-    """x [..., n] at positions pos [T] (x's first axis): pairs (i, i + n/2), angle pos * base^(-2i/n)."""
+def rotate_half(x, pos, base, dims=None):
+    """x [..., m] at positions pos [T] (x's first axis): among the first n = dims columns, pairs (i, i + n/2) turn by
+    the angle pos * base^(-2i/n); the columns behind stay."""
+    if dims is not None and dims < x.shape[-1]:
+        return torch.cat([rotate_half(x[..., :dims], pos, base), x[..., dims:]], -1)
     n = x.shape[-1]
+    if n == 0:
+        return x
     f = base ** (-2.0 * torch.arange(n // 2, dtype=x.dtype) / n)
     a = pos.to(x.dtype)[:, None] * f
     a = a.view(a.shape[0], *([1] * (x.dim() - 2)), n // 2)
@@ -75,16 +80,16 @@ def rotate_half(x, pos, base):
     return torch.cat([u * torch.cos(a) - v * torch.sin(a), v * torch.cos(a) + u * torch.sin(a)], -1)
 
 
-def latent_attention(h, W, state, *, heads, dim, rot_dim, vdim, kv_rank, scale, window, base, eps):
+def latent_attention(h, W, state, *, heads, dim, rot_dim, vdim, kv_rank, scale, window, base, eps, rot_dims=None):
     """W: q, dkv, dkv.norm, uk, uv, o.  `state`: {"c": [n, kv_rank], "kr": [n, rot_dim]} of the tokens before."""
     T = h.shape[0]
     n0 = 0 if "c" not in state else state["c"].shape[0]
     pos = torch.arange(n0, n0 + T)
     q = (h @ W["q"].T).view(T, heads, dim + rot_dim)
-    q_plain, q_rot = q[..., :dim], rotate_half(q[..., dim:], pos, base)
+    q_plain, q_rot = q[..., :dim], rotate_half(q[..., dim:], pos, base, rot_dims)
     d = h @ W["dkv"].T
     c = rms_norm(d[:, :kv_rank], W["dkv.norm"], eps)
-    kr = rotate_half(d[:, kv_rank:], pos, base)
+    kr = rotate_half(d[:, kv_rank:], pos, base, rot_dims)
     if n0:
         c, kr = torch.cat([state["c"], c]), torch.cat([state["kr"], kr])
     state["c"], state["kr"] = c, kr
@@ -172,7 +177,7 @@ class PlainDudurax:
             elif layer["type"] == "latent_attention":
                 y = latent_attention(x, W, st, heads=m["heads"], dim=m["dim"], rot_dim=m["rot_dim"], vdim=m["vdim"],
                                      kv_rank=m["kv_rank"], scale=m["scale"], window=m["mask"]["size"],
-                                     base=m["rot"]["base"], eps=eps)
+                                     base=m["rot"]["base"], eps=eps, rot_dims=m["rot"]["dims"])
             else:
                 raise ValueError(layer["type"])
             x = rms_norm(alpha * x + y, self.w[f"l{i}.norm1"], eps)
