@@ -153,3 +153,234 @@ extern "C" int lb_gla_norm_gate(const float* o, const void* gate, long gate_stri
         o, (const T*)gate, gate_stride, weight, (T*)out, H, vdim, eps));
     return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Prompt portions in chunks of 16 tokens (bfloat16 engines).  With b_i[d] the running sum of the log-decays inside a
+// chunk (inclusive), a chunk that starts from the state S_in gives
+//     o_i   = (q_i * e^{b_i}) S_in  +  sum_{j <= i} A_ij v_j ,     A_ij = sum_d q_i[d] k_j[d] e^{b_i[d] - b_j[d]}
+//     S_out = diag(e^{b_end}) S_in  +  sum_j (k_j * e^{b_end - b_j}) v_j^T
+// and every exponent is <= 0, whatever the decays are: nothing can overflow, and what underflows is truly nothing.
+//
+//  gla_chunk_prepare : one CTA per (chunk, head), all chunks of a step side by side: log-decays and their running sums
+//                      in 32-bit, A in 32-bit (a thread per pair and key-channel slice), the scaled operands
+//                      q * e^{b} and k * e^{b_end - b} rounded to bfloat16 for the tensor cores, e^{b_end} in 32-bit.
+//  gla_chunk_scan    : one CTA per (request, head, 32 value columns) walks the request's chunks in order.  The state
+//                      lives in 32-bit in the accumulator registers of `mma.sync` tiles (rows: key channels) from the
+//                      slot to the slot; per chunk it is scaled by e^{b_end}, takes (k e^{..})^T v on the tensor
+//                      cores, and a bfloat16 copy of it in shared memory is the operand of (q e^{b}) S_in.  The
+//                      chunk's own A v is added in 32-bit.
+constexpr int kChunk = 16;
+constexpr int kScanCols = 32;
+
+__global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(
+        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, long row_stride, const float* __restrict__ z,
+        const int* __restrict__ cu, const int* __restrict__ chunks, __nv_bfloat16* __restrict__ q_in,
+        __nv_bfloat16* __restrict__ k_end, float* __restrict__ A, float* __restrict__ D, int H, int dim, float inv_tau,
+        float q_scale) {
+    extern __shared__ float sm[];
+    float* b = sm;                         // [16][dim] log-decays, then their running sums
+    float* qs = b + kChunk * dim;
+    float* ks = qs + kChunk * dim;
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int req = chunks[2 * c];
+    if (req < 0) return;
+    const int t0 = cu[req] + chunks[2 * c + 1];
+    const int n = min(kChunk, cu[req + 1] - t0);
+    for (int i = threadIdx.x; i < kChunk * dim; i += blockDim.x) {
+        const int j = i / dim, d = i % dim;
+        float ld = 0.f, qv = 0.f, kv = 0.f;
+        if (j < n) {
+            const size_t row = (size_t)(t0 + j);
+            ld = log_sigmoid(z[(row * H + h) * dim + d]) * inv_tau;
+            qv = to_f32(q[row * row_stride + h * dim + d]) * q_scale;
+            kv = to_f32(k[row * row_stride + h * dim + d]);
+        }
+        b[i] = ld; qs[i] = qv; ks[i] = kv;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < kChunk; ++j) { acc += b[j * dim + d]; b[j * dim + d] = acc; }
+        D[((size_t)c * H + h) * dim + d] = expf(acc);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * dim; i += blockDim.x) {
+        const int j = i / dim, d = i % dim;
+        const size_t at = ((size_t)(t0 + j) * H + h) * dim + d;
+        q_in[at] = __float2bfloat16_rn(qs[i] * expf(b[i]));
+        k_end[at] = __float2bfloat16_rn(ks[i] * expf(b[(kChunk - 1) * dim + d] - b[i]));
+    }
+    // A: a warp per pair (i, j), its lanes over the key channels
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int p = warp; p < n * kChunk; p += nwarps) {
+        const int i = p / kChunk, j = p % kChunk;
+        float a = 0.f;
+        if (j <= i)
+            for (int d = lane; d < dim; d += 32) a += qs[i * dim + d] * ks[j * dim + d] * expf(b[i * dim + d] - b[j * dim + d]);
+        a = warp_sum(a);
+        if (lane == 0) A[((size_t)(t0 + i) * H + h) * kChunk + j] = a;
+    }
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+    return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+}
+
+// grid (ceil(vdim / 32), H, long requests); 4 warps; MT: 16-row state tiles per warp (dim <= 64 * MT)
+template <int MT>
+__global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
+        const __nv_bfloat16* __restrict__ q_in, const __nv_bfloat16* __restrict__ k_end, const __nv_bfloat16* __restrict__ v,
+        long v_stride, const float* __restrict__ A, const float* __restrict__ D, float* __restrict__ o, float* state,
+        const int* __restrict__ cu, const int* __restrict__ start_pos, const int* __restrict__ slots,
+        const int* __restrict__ per_request, int H, int dim, int vdim) {
+    constexpr int NT = kScanCols / 8;
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int DP = dim + 8, VP = kScanCols + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(raw);          // [16][DP]
+    __nv_bfloat16* Ks = Qs + kChunk * DP;                                // [16][DP]
+    __nv_bfloat16* Sb = Ks + kChunk * DP;                                // [dim][VP]
+    __nv_bfloat16* Vs = Sb + dim * VP;                                   // [16][VP]
+    float* As = reinterpret_cast<float*>(Vs + kChunk * VP);              // [16][16]
+    float* Ds = As + kChunk * kChunk;                                    // [dim]
+    const int req = per_request[3 * blockIdx.z];
+    if (req < 0) return;
+    const int chunk0 = per_request[3 * blockIdx.z + 1], nchunks = per_request[3 * blockIdx.z + 2];
+    const int h = blockIdx.y, col0 = blockIdx.x * kScanCols;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int first = cu[req], last = cu[req + 1];
+    const size_t sbase = ((size_t)slots[req] * H + h) * dim * vdim;
+    const bool fresh = start_pos[req] == 0;
+    float S[MT][NT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int d = (warp * MT + m) * 16 + g + (e >> 1) * 8, c = col0 + nt * 8 + 2 * t + (e & 1);
+                S[m][nt][e] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
+            }
+    for (int ci = 0; ci < nchunks; ++ci) {
+        const int t0 = first + ci * kChunk;
+        const int n = min(kChunk, last - t0);
+        __syncthreads();                                   // the chunk before is done with the shared tiles
+        for (int i = threadIdx.x; i < kChunk * dim; i += blockDim.x) {
+            const int j = i / dim, d = i % dim;
+            const size_t at = ((size_t)(t0 + j) * H + h) * dim + d;
+            Qs[j * DP + d] = j < n ? q_in[at] : __float2bfloat16_rn(0.f);
+            Ks[j * DP + d] = j < n ? k_end[at] : __float2bfloat16_rn(0.f);
+        }
+        for (int i = threadIdx.x; i < kChunk * kScanCols; i += blockDim.x) {
+            const int j = i / kScanCols, c = i % kScanCols;
+            Vs[j * VP + c] = (j < n && col0 + c < vdim) ? v[(size_t)(t0 + j) * v_stride + h * vdim + col0 + c] : __float2bfloat16_rn(0.f);
+        }
+        for (int i = threadIdx.x; i < kChunk * kChunk; i += blockDim.x) {
+            const int r = i / kChunk;
+            As[i] = r < n ? A[((size_t)(t0 + r) * H + h) * kChunk + i % kChunk] : 0.f;
+        }
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) Ds[d] = D[((size_t)(chunk0 + ci) * H + h) * dim + d];
+        // the state as it stands before this chunk, rounded, as the operand of the output product
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int r0 = (warp * MT + m) * 16 + g;
+            if (r0 - g < dim) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int c = nt * 8 + 2 * t;
+                    *reinterpret_cast<__nv_bfloat162*>(Sb + r0 * VP + c) = __floats2bfloat162_rn(S[m][nt][0], S[m][nt][1]);
+                    *reinterpret_cast<__nv_bfloat162*>(Sb + (r0 + 8) * VP + c) = __floats2bfloat162_rn(S[m][nt][2], S[m][nt][3]);
+                }
+            }
+        }
+        __syncthreads();
+        // o[16 tokens][8 columns of this warp] = Qs Sb + As Vs
+        {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const int cw = warp * 8;
+            for (int kk = 0; kk < dim; kk += 16) {
+                uint32_t a[4];
+                a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t);
+                a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t);
+                a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t + 8);
+                const uint32_t b0 = pack2(Sb[(kk + 2 * t) * VP + cw + g], Sb[(kk + 2 * t + 1) * VP + cw + g]);
+                const uint32_t b1 = pack2(Sb[(kk + 2 * t + 8) * VP + cw + g], Sb[(kk + 2 * t + 9) * VP + cw + g]);
+                mma_bf16_16816(acc, a, b0, b1);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = g + (e >> 1) * 8, c = cw + 2 * t + (e & 1);
+                float s = acc[e];
+                for (int j = 0; j <= i; ++j) s += As[i * kChunk + j] * to_f32(Vs[j * VP + c]);
+                if (i < n && col0 + c < vdim) o[((size_t)(t0 + i) * H + h) * vdim + col0 + c] = s;
+            }
+        }
+        // S <- diag(D) S + Ks^T Vs
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int r0 = (warp * MT + m) * 16 + g;
+            if (r0 - g < dim) {
+                const float d0 = Ds[r0], d1 = Ds[r0 + 8];
+                uint32_t a[4];
+                a[0] = pack2(Ks[(2 * t) * DP + r0], Ks[(2 * t + 1) * DP + r0]);
+                a[1] = pack2(Ks[(2 * t) * DP + r0 + 8], Ks[(2 * t + 1) * DP + r0 + 8]);
+                a[2] = pack2(Ks[(2 * t + 8) * DP + r0], Ks[(2 * t + 9) * DP + r0]);
+                a[3] = pack2(Ks[(2 * t + 8) * DP + r0 + 8], Ks[(2 * t + 9) * DP + r0 + 8]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    S[m][nt][0] *= d0; S[m][nt][1] *= d0; S[m][nt][2] *= d1; S[m][nt][3] *= d1;
+                    const uint32_t b0 = pack2(Vs[(2 * t) * VP + nt * 8 + g], Vs[(2 * t + 1) * VP + nt * 8 + g]);
+                    const uint32_t b1 = pack2(Vs[(2 * t + 8) * VP + nt * 8 + g], Vs[(2 * t + 9) * VP + nt * 8 + g]);
+                    mma_bf16_16816(S[m][nt], a, b0, b1);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int d = (warp * MT + m) * 16 + g + (e >> 1) * 8, c = col0 + nt * 8 + 2 * t + (e & 1);
+                if (d < dim && c < vdim) state[sbase + (size_t)d * vdim + c] = S[m][nt][e];
+            }
+}
+
+// Chunked form over the long portions of a step (bfloat16).  q, k, v: column views of one projection buffer; z as for
+// the scan; chunks: int32 [num_chunks, 2] (request, first token within its portion; request -1: nothing);
+// per_request: int32 [num_long, 3] (request, its first chunk, its number of chunks).  Scratch: q_in, k_end
+// [tokens, H, dim] bfloat16, A float32 [tokens, H, 16], D float32 [num_chunks, H, dim].  dim: a multiple of 16, <= 256.
+extern "C" int lb_gla_chunked(const void* q, const void* k, const void* v, long row_stride, const float* z, float* o, float* state,
+                              const int* cu, const int* start_pos, const int* slots, const int* chunks, int num_chunks,
+                              const int* per_request, int num_long, void* q_in, void* k_end, float* A, float* D, int H, int dim,
+                              int vdim, float tau, float q_scale, void* stream) {
+    if (num_chunks <= 0 || num_long <= 0) return kOk;
+    if (H <= 0 || dim <= 0 || vdim <= 0 || !(tau > 0.f) || dim % 16) return kBadSize;
+    if (dim > 256) return kTooLarge;
+    cudaStream_t st = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+    {
+        const size_t smem = (size_t)3 * kChunk * dim * sizeof(float);
+        static size_t have = 0;
+        ensure_dynamic_smem(gla_chunk_prepare_kernel, smem, have);
+        gla_chunk_prepare_kernel<<<dim3(num_chunks, H), 128, smem, st>>>((const bf*)q, (const bf*)k, row_stride, z, cu, chunks,
+                                                                        (bf*)q_in, (bf*)k_end, A, D, H, dim, 1.f / tau, q_scale);
+        const int rc = launch_status();
+        if (rc != 0) return rc;
+    }
+    const size_t smem = ((size_t)2 * kChunk * (dim + 8) + (size_t)dim * (kScanCols + 8) + (size_t)kChunk * (kScanCols + 8)) * sizeof(bf)
+                        + ((size_t)kChunk * kChunk + dim) * sizeof(float);
+    dim3 grid((vdim + kScanCols - 1) / kScanCols, H, num_long);
+#define LB_SCAN(MT_) { static size_t have = 0; ensure_dynamic_smem(gla_chunk_scan_kernel<MT_>, smem, have); \
+        gla_chunk_scan_kernel<MT_><<<grid, 128, smem, st>>>((const bf*)q_in, (const bf*)k_end, (const bf*)v, row_stride, A, D, o, state, \
+                                                           cu, start_pos, slots, per_request, H, dim, vdim); }
+    if (dim <= 64) LB_SCAN(1) else if (dim <= 128) LB_SCAN(2) else LB_SCAN(4)
+#undef LB_SCAN
+    return launch_status();
+}

@@ -1099,6 +1099,48 @@ def gla_scan(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens
     return o
 
 
+GLA_CHUNKED = os.environ.get("LOGSSMS_B200_GLA_CHUNKED", "1") != "0"
+GLA_CHUNK = 16
+
+
+def gla_chunked_ok(qkv: torch.Tensor, key_dim: int) -> bool:
+    """Does the chunked form take these operands (else: the token-by-token scan)?  bfloat16, key channels a multiple of 16
+    up to 256."""
+    return GLA_CHUNKED and qkv.dtype == torch.bfloat16 and key_dim % 16 == 0 and key_dim <= 256
+
+
+def gla_chunked(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+                slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int, per_request: torch.Tensor, num_long: int,
+                num_heads: int, key_dim: int, value_dim: int, tau: float, q_scale: float, out: torch.Tensor) -> torch.Tensor:
+    """The recurrence of `gla_scan` over the long portions of a step in chunks of `GLA_CHUNK` tokens on the tensor cores
+    (see `csrc/gla.cu`); the rows of the other requests in `out` (float32 [tokens, H*value_dim]) are left alone.
+    `chunks`, `per_request`: the work lists of `StepContext.long_portion_chunks(GLA_CHUNK)`."""
+    _cuda(qkv, z, state, cu_seqlens, start_pos, slots, chunks, per_request, out)
+    H, dk, dv = num_heads, key_dim, value_dim
+    T = qkv.shape[0]
+    _need(gla_chunked_ok(qkv, dk), "gla_chunked takes bfloat16 operands with key channels a multiple of 16 up to 256")
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= H * (2 * dk + dv), "qkv must hold the columns q | k | v")
+    _need(z.dtype == torch.float32 and z.shape == (T, H * dk) and z.is_contiguous(), "z must be contiguous float32 [tokens, H*key_dim]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dk, dv),
+          "the state must be contiguous float32 [slots, H, key_dim, value_dim]")
+    _need(out.dtype == torch.float32 and out.shape == (T, H * dv) and out.is_contiguous(), "out must be contiguous float32 [tokens, H*value_dim]")
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots"), (chunks, "chunks"), (per_request, "per_request")):
+        _i32(t, name)
+    q_in = torch.empty((T, H, dk), dtype=torch.bfloat16, device=qkv.device)
+    k_end = torch.empty((T, H, dk), dtype=torch.bfloat16, device=qkv.device)
+    A = torch.empty((T, H, GLA_CHUNK), dtype=torch.float32, device=qkv.device)
+    D = torch.empty((max(num_chunks, 1), H, dk), dtype=torch.float32, device=qkv.device)
+    item, base = qkv.element_size(), qkv.data_ptr()
+    f = _fn("gla", "lb_gla_chunked", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_float, c_float, c_void_p])
+    _check(f(base, base + H * dk * item, base + 2 * H * dk * item, qkv.stride(0) if T > 1 else qkv.shape[1], _ptr(z), _ptr(out),
+             _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(per_request), num_long,
+             _ptr(q_in), _ptr(k_end), _ptr(A), _ptr(D), H, dk, dv, tau, q_scale, _stream()), "gla_chunked",
+           f"(key_dim {dk}, value_dim {dv})", launches=2)
+    return out
+
+
 def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, num_heads: int) -> torch.Tensor:
     """RMSNorm of every head's float32 output with one weight [value_dim] for all heads, times silu(gate); the result
     has the gate's dtype.  `gate` may be a column view of a wider matrix."""

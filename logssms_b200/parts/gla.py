@@ -15,7 +15,8 @@ class GatedLinearAttention(Part):
     sigmoid(z)^(1/tau) per key channel.  Per head S <- diag(decay) S + k v^T, o = S^T q / sqrt(key_dim); o is
     RMS-normed per head (one weight [value_dim] for all heads), times silu(g), then the output projection.
 
-    Per-request state: S [heads, key_dim, value_dim] in float32.  The five input projections are one product
+    Per-request state: S [heads, key_dim, value_dim] in float32.  Prompt portions of a bfloat16 engine run in chunks of
+    16 tokens on the tensor cores (`K.gla_chunked`), everything else token by token (`K.gla_scan`).  The five input projections are one product
     (rows q | k | v | g | a1, merged at bind time).  Decay, state and the head norm are 32-bit in every engine dtype.
     Tensors: q, k, v, g, o, norm, a1, a2, a2.b."""
     kernels = ("gla", "linear_skinny", "gemm_tcgen05")
@@ -64,7 +65,19 @@ class GatedLinearAttention(Part):
         low = proj[:, 2 * qk + 2 * vg:]
         z = K.linear(low, self.a2_w, self.a2_b, out_f32=True)
         state = ctx.cache.states[cache_layer]["gla"]
-        o = K.gla_scan(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, ctx.num_requests, s.num_heads,
-                       s.key_dim, s.value_dim, s.tau, s.key_dim ** -0.5)
+        sizes = (s.num_heads, s.key_dim, s.value_dim, s.tau, s.key_dim ** -0.5)
+        if ctx.has_long_portions and K.gla_chunked_ok(proj, s.key_dim):
+            # long portions in chunks on the tensor cores; decoded tokens and short portions (other requests, other rows
+            # of o) token by token
+            chunks, n_chunks, per_request, n_long = ctx.long_portion_chunks(K.GLA_CHUNK)
+            _, _, short_list, n_short = ctx.requests_by_portion()
+            o = torch.empty((x.shape[0], vg), dtype=torch.float32, device=x.device)
+            K.gla_chunked(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, chunks, n_chunks, per_request, n_long,
+                          *sizes, out=o)
+            if n_short > 0:
+                K.gla_scan(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, ctx.num_requests, *sizes,
+                           request_list=short_list, out=o)
+        else:
+            o = K.gla_scan(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, ctx.num_requests, *sizes)
         y = K.gla_norm_gate(o, proj[:, 2 * qk + vg: 2 * qk + 2 * vg], self.norm_w, s.norm_eps, s.num_heads)
         return K.linear(y, self.o_w)

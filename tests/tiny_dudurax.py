@@ -75,7 +75,7 @@ def make_dudurax_dir(path, raw: dict, seed: int = 0, dtype=torch.float32, sharp:
             t[name] = (t[name].float() * sharp).to(t[name].dtype)
         if steady_router and name.endswith(".mlp.correction"):
             n = t[name].numel()
-            t[name] = (0.25 * torch.randperm(n, generator=gen).float()).to(t[name].dtype)
+            t[name] = (1.5 * torch.randperm(n, generator=gen).float()).to(t[name].dtype)
     save_file(t, file)
     return out
 
@@ -100,4 +100,4 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return d.pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-30)
 
 
-TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+TOL = {"float32": 1e-4, "bfloat16": 5e-2}
