@@ -733,6 +733,118 @@ def run_probe(args) -> int:
         shutil.rmtree(tmp, ignore_errors=True)
 
 
+# --------------------------------------------------------------------------- another design beside the closest one
+def _dudurax_config(width: int, layers: int, heads: int, key_dim: int, value_dim: int, kv_rank: int, rot: int, window: int,
+                    experts: int, top: int, expert_ff: int, dense_ff: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: three gated-linear-attention layers to one latent-attention layer,
+    routed feed-forwards with one dense one in front."""
+    gla = lambda kind: {"type": kind, "mixer": {"heads": heads, "dim": key_dim, "vdim": value_dim, "tau": 16.0, "decay_rank": 16}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": key_dim, "rot_dim": rot, "vdim": key_dim, "kv_rank": kv_rank, "mask": {"size": window},
+                        "rot": {"base": 10000.0, "dims": rot}, "scale": (key_dim + rot) ** -0.5}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0},
+           "router": {"experts": experts, "identity": 2, "groups": {"count": 2, "keep": 2}, "top": top, "scale": 1.0}}
+    out = []
+    for i in range(layers):
+        mixer = latent if i % 4 == 3 else gla("gla" if i % 2 else "gla_2")
+        out.append({**mixer, "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe})
+    return {"architecture": "Dudurax", "embedding": {"bigram": {"buckets": 65521, "mul_cur": 17, "mul_prev": 127}, "scale": 8.0},
+            "layers": out, "norm": {"eps": 1e-5}, "postln_alpha": 2.0, "vocab": vocab, "width": width}
+
+
+# (name, the new design's configuration, the closest existing model at the same width and depth)
+DESIGN_SIZES = {
+    "w1024": (_dudurax_config(1024, 4, 8, 64, 128, 256, 32, 1024, 8, 2, 1024, 2048, 32768),
+              {**MODELS["0p5b"], "num_hidden_layers": 4, "vocab_size": 32768}),
+    "w2048": (_dudurax_config(2048, 4, 16, 128, 128, 512, 64, 2048, 16, 4, 1408, 8192, 65536),
+              {**_COMMON, "num_hidden_layers": 4, "hidden_size": 2048, "num_attention_heads": 16, "num_key_value_heads": 4,
+               "head_dim": 128, "intermediate_size": 8192, "vocab_size": 65536, "max_position_embeddings": 8192,
+               "tie_word_embeddings": False, "mamba_d_ssm": 3072, "mamba_n_heads": 24, "mamba_d_head": 128, "mamba_d_state": 128}),
+}
+
+
+def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: int) -> dict:
+    """Prefill (one prompt of PREFILL_TOKENS as one step) and decode (batch x one token from `context`-token contexts) of
+    one random-weights model through `Engine.step`, timed with CUDA events after W warm-up steps; then the same steps
+    once more kernel by kernel with every kernel timed (`profile`)."""
+    import numpy as np
+    import torch
+    from logssms_b200.config import make_model_config
+    from logssms_b200.engine import Engine, StepEntry
+    from logssms_b200.ops import kernels
+    from logssms_b200.weights import write_random_model
+
+    tmp = tempfile.mkdtemp(prefix="logssms_b200_design_")
+    out: dict = {}
+    try:
+        write_random_model(make_model_config(cfg), tmp, seed=0, dtype=torch.bfloat16)
+        rng = np.random.default_rng(0)
+        flush = torch.empty(160 << 20, dtype=torch.uint8, device="cuda")          # larger than L2, written between timed steps
+
+        def timed(engine, make_entries, n, warm):
+            times = []
+            for i in range(warm + n):
+                entries, after = make_entries()
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                engine.step(entries)
+                b.record()
+                torch.cuda.synchronize()
+                after()
+                if i >= warm:
+                    times.append(a.elapsed_time(b))
+            kernels.check_kernel_errors(engine.device)
+            return float(np.median(times))
+
+        for profile in (False, True):
+            engine = Engine(tmp, "bfloat16", max_requests=max(batch, 8), max_seq_len=context + 256, page_size=64, profile=profile)
+
+            def prompt():
+                r = engine.new_request()
+                return [StepEntry(r, rng.integers(0, vocab, PREFILL_TOKENS).tolist(), [PREFILL_TOKENS - 1])], lambda: engine.release(r)
+            if not profile:
+                ms = timed(engine, prompt, K, max(W, 4))
+                out["prefill"] = {"tokens": PREFILL_TOKENS, "ms": round(ms, 3), "tok_per_s": round(PREFILL_TOKENS / ms * 1e3)}
+            else:
+                timed(engine, prompt, 2, 1)
+                out["prefill_kernels"] = engine.profile_report()
+                from logssms_b200.ops.profiler import PROFILER
+                PROFILER.reset()
+            reqs = [engine.new_request() for _ in range(batch)]
+            for r in reqs:
+                engine.step([StepEntry(r, rng.integers(0, vocab, context).tolist(), [])])
+            single = lambda: ([StepEntry(r, [int(rng.integers(0, vocab))], [0]) for r in reqs], lambda: None)
+            if not profile:
+                ms = timed(engine, single, K, max(W, 4))
+                out["decode"] = {"batch": batch, "context": context, "ms": round(ms, 3), "tok_per_s": round(batch / ms * 1e3)}
+            else:
+                from logssms_b200.ops.profiler import PROFILER
+                PROFILER.reset()
+                timed(engine, single, 3, 1)
+                out["decode_kernels"] = engine.profile_report()
+            del engine, reqs
+            torch.cuda.empty_cache()
+        return out
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+def run_design(args) -> dict:
+    """`--design dudurax`: the Dudurax design at a few layer sizes beside Falcon-H1 at the same width and depth."""
+    sizes = {}
+    for name, (new, closest) in DESIGN_SIZES.items():
+        log(f"design sizes {name}: dudurax")
+        ours = _design_point(new, new["vocab"], args.steps, args.warmup, args.batch, CONTEXT)
+        log(f"design sizes {name}: falcon-h1")
+        base = _design_point(closest, closest["vocab_size"], args.steps, args.warmup, args.batch, CONTEXT)
+        sizes[name] = {"dudurax": ours, "falcon_h1": base, "layers": len(new["layers"]), "width": new["width"]}
+    pk, src = peaks()
+    return {"design": "dudurax", "beside": "falcon_h1", "dtype": "bf16", "data": "synthetic", "peaks": {**pk, "source": src},
+            "timing": "CUDA events around Engine.step, median; L2 flushed between steps", "sizes": sizes}
+
+
 # --------------------------------------------------------------------------- the reference arm
 def run_reference(args) -> dict:
     """The reference runs in a child process (its own CUDA context, streams and JIT caches), with a time
@@ -780,6 +892,9 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
     ap.add_argument("--probe", choices=["decode", "prefill", "mixed"], default=None,
                     help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
+    ap.add_argument("--design", choices=["dudurax"], default=None,
+                    help="prefill and decode of another design at a few layer sizes beside the closest existing model "
+                         "(one JSON line of its own; the default workload is untouched)")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print("bench.py: this engine runs on one GPU; --gpus N>1 is not built")
@@ -788,6 +903,9 @@ def main() -> int:
         args.warmup = 3
     if args.probe:
         return run_probe(args)
+    if args.design:
+        print(json.dumps(run_design(args)))
+        return 0
     if args.impl == "reference":
         try:
             line = run_reference(args)

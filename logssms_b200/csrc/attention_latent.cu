@@ -206,3 +206,238 @@ extern "C" int lb_latent_attention(const void* qa, const void* q_rot, long q_rot
     });
     return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16; rank a multiple of 32 up to 512, rot a multiple of 16).
+//
+// All heads of a token read the same cached rows, so the 16 rows of an `mma.sync` tile are (token, head) pairs that
+// share their keys: 16 heads of one token, or 16 / H neighbouring tokens of one request with all their H heads.  A CTA
+// of four warps owns one such tile and one range of its keys (`splits` ranges per tile: a decode step has few tiles).
+// Per 32 keys, staged once in shared memory as [c | kr] rows: every warp computes the scores of 8 of the keys over
+// the whole row length rank + rot, the row maxima meet in shared memory, the weights (32-bit, then rounded for the
+// product) go to shared memory, and every warp multiplies them with its quarter of the c columns; the running output
+// stays in registers.  Scores, maxima, weights and sums are 32-bit.  With one range the CTA writes the output, else
+// its unnormalised part with the row's maximum and sum, which `latent_merge` puts together.
+constexpr int kMmaKeys = 32;
+
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
+    return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+}
+
+// grid (token blocks, head groups, splits); NTW: 8-column output tiles per warp (rank <= 32 * NTW)
+template <int NTW>
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(
+        const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ q_rot, long q_rot_row, long q_rot_head,
+        const __nv_bfloat16* __restrict__ c_cache, const __nv_bfloat16* __restrict__ kr_cache,
+        const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
+        const int* __restrict__ positions, const int* __restrict__ blocks, __nv_bfloat16* __restrict__ out,
+        float* __restrict__ part_o, float* __restrict__ part_ml, int H, int rank, int rot, int page_size, float scale,
+        int window, int splits) {
+    typedef __nv_bfloat16 bf;
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int D = rank + rot, DP = D + 8, PP = kMmaKeys + 8;
+    bf* Qs = reinterpret_cast<bf*>(raw);                    // [16][DP]
+    bf* Kt = Qs + 16 * DP;                                  // [32][DP]
+    bf* Ps = Kt + kMmaKeys * DP;                            // [16][PP]
+    float* red = reinterpret_cast<float*>(Ps + 16 * PP);    // [4][16]
+    __shared__ int row_lo[16], row_hi[16];
+    const int t0 = blocks ? blocks[2 * blockIdx.x] : blockIdx.x, ntok = blocks ? blocks[2 * blockIdx.x + 1] : 1;
+    if (t0 < 0) return;
+    const int nh = H >= 16 ? min(16, H - (int)blockIdx.y * 16) : H;       // heads of this tile
+    const int h0 = H >= 16 ? blockIdx.y * 16 : 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int* pages = block_table + (size_t)token_req[t0] * table_width;
+    if (threadIdx.x < 16) {
+        const int r = threadIdx.x, tok = r / nh;
+        int lo = 1, hi = 0;                                  // an empty range: a row without a token
+        if (tok < ntok) {
+            hi = positions[t0 + tok];
+            lo = window > 0 ? max(0, hi - window + 1) : 0;
+        }
+        row_lo[r] = lo; row_hi[r] = hi;
+    }
+    for (int i = threadIdx.x; i < 16 * D; i += blockDim.x) {
+        const int r = i / D, d = i % D, tok = r / nh, h = h0 + r % nh;
+        bf v = __float2bfloat16_rn(0.f);
+        if (tok < ntok)
+            v = d < rank ? qa[((size_t)(t0 + tok) * H + h) * rank + d]
+                         : q_rot[(size_t)(t0 + tok) * q_rot_row + (size_t)h * q_rot_head + d - rank];
+        Qs[r * DP + d] = v;
+    }
+    const int p_hi = positions[t0 + ntok - 1], p_first = positions[t0];
+    const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int tiles = (p_hi - key_lo + kMmaKeys) / kMmaKeys;
+    const int per = (tiles + splits - 1) / splits;
+    const int tile_lo = blockIdx.z * per, tile_hi = min(tiles, tile_lo + per);
+    float acc[NTW][4];
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int ntw = rank / 32;                               // output tiles of this warp
+    const int colw = warp * (rank / 4);
+    __syncthreads();
+    const int lo0 = row_lo[g], hi0 = row_hi[g], lo1 = row_lo[g + 8], hi1 = row_hi[g + 8];
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+        const int j0 = key_lo + tile * kMmaKeys;
+        __syncthreads();                                     // the tile before is used up
+        for (int jj = warp; jj < kMmaKeys; jj += 4) {
+            const int j = j0 + jj;
+            uint4* dst = reinterpret_cast<uint4*>(Kt + jj * DP);
+            if (j <= p_hi) {
+                const size_t off = (size_t)pages[j / page_size] * page_size + j % page_size;
+                const uint4* c4 = reinterpret_cast<const uint4*>(c_cache + off * rank);
+                const uint4* k4 = reinterpret_cast<const uint4*>(kr_cache + off * rot);
+                for (int i = lane; i < rank / 8; i += 32) dst[i] = c4[i];
+                for (int i = lane; i < rot / 8; i += 32) dst[rank / 8 + i] = k4[i];
+            } else {
+                for (int i = lane; i < D / 8; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        __syncthreads();
+        // scores of this warp's 8 keys
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf* kb = Kt + (warp * 8 + g) * DP;
+        for (int kk = 0; kk < D; kk += 16) {
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t);
+            a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t);
+            a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t + 8);
+            mma_16816(s, a, *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t), *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t + 8));
+        }
+        const int jk = j0 + warp * 8 + 2 * t;
+        s[0] = (jk >= lo0 && jk <= hi0) ? s[0] * scale : -INFINITY;
+        s[1] = (jk + 1 >= lo0 && jk + 1 <= hi0) ? s[1] * scale : -INFINITY;
+        s[2] = (jk >= lo1 && jk <= hi1) ? s[2] * scale : -INFINITY;
+        s[3] = (jk + 1 >= lo1 && jk + 1 <= hi1) ? s[3] * scale : -INFINITY;
+        float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (t == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
+        __syncthreads();
+        float corr[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = g + 8 * e;
+            const float mt = fmaxf(fmaxf(red[r], red[16 + r]), fmaxf(red[32 + r], red[48 + r]));
+            const float mn = fmaxf(m[e], mt);
+            corr[e] = (mn == -INFINITY) ? 1.f : expf(m[e] - mn);
+            m[e] = mn;
+        }
+        const float p0 = m[0] == -INFINITY ? 0.f : expf(s[0] - m[0]), p1 = m[0] == -INFINITY ? 0.f : expf(s[1] - m[0]);
+        const float p2 = m[1] == -INFINITY ? 0.f : expf(s[2] - m[1]), p3 = m[1] == -INFINITY ? 0.f : expf(s[3] - m[1]);
+        const __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + g * PP + warp * 8 + 2 * t) = pa;
+        *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * PP + warp * 8 + 2 * t) = pb;
+        // the sums take the weights as the product sees them
+        l[0] = l[0] * corr[0] + __bfloat162float(pa.x) + __bfloat162float(pa.y);
+        l[1] = l[1] * corr[1] + __bfloat162float(pb.x) + __bfloat162float(pb.y);
+        __syncthreads();
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            if (nt < ntw) { acc[nt][0] *= corr[0]; acc[nt][1] *= corr[0]; acc[nt][2] *= corr[1]; acc[nt][3] *= corr[1]; }
+        }
+#pragma unroll
+        for (int ks = 0; ks < kMmaKeys; ks += 16) {
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(Ps + g * PP + ks + 2 * t);
+            a[1] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * PP + ks + 2 * t);
+            a[2] = *reinterpret_cast<const uint32_t*>(Ps + g * PP + ks + 2 * t + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * PP + ks + 2 * t + 8);
+            const bf* v0 = Kt + (ks + 2 * t) * DP + colw + g;
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt) {
+                if (nt < ntw) {
+                    const bf* vp = v0 + nt * 8;
+                    mma_16816(acc[nt], a, pack_bf16(vp[0], vp[DP]), pack_bf16(vp[8 * DP], vp[9 * DP]));
+                }
+            }
+        }
+    }
+    // the rows' sums: over the four lanes that share a row, then over the warps
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
+    }
+    if (t == 0) { red[warp * 16 + g] = l[0]; red[warp * 16 + g + 8] = l[1]; }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int r = g + 8 * e, tok = r / nh, h = h0 + r % nh;
+        if (tok >= ntok) continue;
+        const float lt = red[r] + red[16 + r] + red[32 + r] + red[48 + r];
+        const size_t row = (size_t)(t0 + tok) * H + h;
+        if (splits == 1) {
+            const float inv = lt > 0.f ? 1.f / lt : 0.f;
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt)
+                if (nt < ntw)
+                    *reinterpret_cast<__nv_bfloat162*>(out + row * rank + colw + nt * 8 + 2 * t) =
+                        __floats2bfloat162_rn(acc[nt][2 * e] * inv, acc[nt][2 * e + 1] * inv);
+        } else {
+            float* po = part_o + (row * splits + blockIdx.z) * rank + colw;
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt)
+                if (nt < ntw) { po[nt * 8 + 2 * t] = acc[nt][2 * e]; po[nt * 8 + 2 * t + 1] = acc[nt][2 * e + 1]; }
+            if (warp == 0 && t == 0) {
+                part_ml[(row * splits + blockIdx.z) * 2] = m[e];
+                part_ml[(row * splits + blockIdx.z) * 2 + 1] = lt;
+            }
+        }
+    }
+}
+
+// grid (listed token blocks' rows): one CTA per (token, head) row of the step
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, int rank, int splits) {
+    const size_t row = blockIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(row * splits + s) * 2]);
+    if (M == -INFINITY) return;                              // a row that no block of this step owns
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += part_ml[(row * splits + s) * 2 + 1] * expf(part_ml[(row * splits + s) * 2] - M);
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(row * splits + s) * 2];
+            if (ms != -INFINITY) a += part_o[(row * splits + s) * rank + c] * expf(ms - M);
+        }
+        out[row * rank + c] = __float2bfloat16_rn(a / L);
+    }
+}
+
+// blocks: int32 [num_blocks, 2] (first token row, tokens: neighbours of one request, at most max(1, 16 / H); -1: nothing),
+// or null: every token a block of its own (num_blocks = tokens).
+// Every token of the step lies in exactly one block.  part_o float32 [tokens * H, splits, rank] and part_ml float32
+// [tokens * H, splits, 2]: scratch for splits > 1 (every row is written by the CTAs of its block).
+extern "C" int lb_latent_attention_mma(const void* qa, const void* q_rot, long q_rot_row, long q_rot_head, const void* c_cache,
+                                       const void* kr_cache, const int* block_table, int table_width, const int* token_req,
+                                       const int* positions, const int* blocks, int num_blocks, void* out, float* part_o,
+                                       float* part_ml, int tokens, int H, int rank, int rot, int page_size, float scale,
+                                       int window, int splits, void* stream) {
+    if (num_blocks <= 0) return kOk;
+    if (H <= 0 || rank <= 0 || rank % 32 || rot < 0 || rot % 16 || page_size <= 0 || window < 0 || splits < 1) return kBadSize;
+    if (rank > 512 || splits > 65535) return kTooLarge;
+    typedef __nv_bfloat16 bf;
+    const int D = rank + rot;
+    const size_t smem = ((size_t)(16 + kMmaKeys) * (D + 8) + 16 * (kMmaKeys + 8)) * sizeof(bf) + 64 * sizeof(float);
+    dim3 grid(num_blocks, H >= 16 ? (H + 15) / 16 : 1, splits);
+    cudaStream_t st = (cudaStream_t)stream;
+#define LB_LA(NTW_) { static size_t have = 0; ensure_dynamic_smem(latent_attention_mma_kernel<NTW_>, smem, have); \
+        latent_attention_mma_kernel<NTW_><<<grid, 128, smem, st>>>((const bf*)qa, (const bf*)q_rot, q_rot_row, q_rot_head, \
+            (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, part_o, \
+            part_ml, H, rank, rot, page_size, scale, window, splits); }
+    if (rank <= 128) LB_LA(4) else if (rank <= 256) LB_LA(8) else LB_LA(16)
+#undef LB_LA
+    int rc = launch_status();
+    if (rc != 0 || splits == 1) return rc;
+    latent_merge_kernel<<<tokens * H, 128, 0, st>>>(part_o, part_ml, (bf*)out, rank, splits);
+    return launch_status();
+}

@@ -15,30 +15,37 @@
 using namespace lb200;
 
 constexpr int kRouteMax = 256;        // router outputs
-constexpr int kRouteWarps = 4;        // tokens per CTA
+constexpr int kRouteWarps = 4;        // warps of a token's CTA: each takes every fourth router output
 
+// grid (tokens)
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
-                                 float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_w,
-                                 float* __restrict__ id_weight, int tokens, int width, int n, int experts, int top,
-                                 int groups, int keep, float scale) {
-    __shared__ float zs[kRouteWarps][kRouteMax];
-    __shared__ float cs[kRouteWarps][kRouteMax];
-    __shared__ unsigned char ok[kRouteWarps][kRouteMax];
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
+        const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
+        float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_w,
+        float* __restrict__ id_weight, int tokens, int width, int n, int experts, int top,
+        int groups, int keep, float scale) {
+    __shared__ float z[kRouteMax];
+    __shared__ float c[kRouteMax];
+    __shared__ unsigned char ok[kRouteMax];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * kRouteWarps + warp;
-    if (t >= tokens) return;
+    const int t = blockIdx.x;
     const T* hr = h + (size_t)t * width;
-    float* z = zs[warp];
-    float* c = cs[warp];
-    for (int e = 0; e < n; ++e) {
+    for (int e = warp; e < n; e += kRouteWarps) {
         const float* wr = w_router + (size_t)e * width;
-        float a = 0.f;
-        for (int k = lane; k < width; k += 32) a += to_f32(hr[k]) * wr[k];
-        a = warp_sum(a);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int k = lane;
+        for (; k + 96 < width; k += 128) {
+            a0 += to_f32(hr[k]) * wr[k];
+            a1 += to_f32(hr[k + 32]) * wr[k + 32];
+            a2 += to_f32(hr[k + 64]) * wr[k + 64];
+            a3 += to_f32(hr[k + 96]) * wr[k + 96];
+        }
+        for (; k < width; k += 32) a0 += to_f32(hr[k]) * wr[k];
+        const float a = warp_sum((a0 + a1) + (a2 + a3));
         if (lane == 0) z[e] = a;
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     float mx = -INFINITY;
     for (int e = lane; e < n; e += 32) mx = fmaxf(mx, z[e]);
     mx = warp_max(mx);
@@ -50,7 +57,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         const float s = expf(z[e] - mx) / sum;
         z[e] = s;
         c[e] = s + correction[e];
-        ok[warp][e] = 0;
+        ok[e] = 0;
         dense[(size_t)t * n + e] = 0.f;
     }
     __syncwarp();
@@ -61,22 +68,22 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         int best_g = -1;
         float best = -INFINITY;
         for (int g = 0; g < groups; ++g) {
-            if (ok[warp][g * per]) continue;
+            if (ok[g * per]) continue;
             float gm = -INFINITY;
             for (int i = 0; i < per; ++i) gm = fmaxf(gm, c[g * per + i]);
             if (best_g < 0 || gm > best) { best = gm; best_g = g; }
         }
         if (best_g < 0) break;
-        for (int i = 0; i < per; ++i) ok[warp][best_g * per + i] = 1;
+        for (int i = 0; i < per; ++i) ok[best_g * per + i] = 1;
     }
     float idw = 0.f;
     for (int r = 0; r < top; ++r) {
         int best_e = -1;
         float best = -INFINITY;
         for (int e = 0; e < n; ++e)
-            if (ok[warp][e] == 1 && (best_e < 0 || c[e] > best)) { best = c[e]; best_e = e; }
+            if (ok[e] == 1 && (best_e < 0 || c[e] > best)) { best = c[e]; best_e = e; }
         if (best_e < 0) { chosen[(size_t)t * top + r] = -1; chosen_w[(size_t)t * top + r] = 0.f; continue; }
-        ok[warp][best_e] = 2;
+        ok[best_e] = 2;
         const float wgt = z[best_e] * scale;
         dense[(size_t)t * n + best_e] = wgt;
         chosen[(size_t)t * top + r] = best_e;
@@ -93,8 +100,7 @@ extern "C" int lb_moe_route(const void* h, const float* w_router, const float* c
     if (n <= 0 || experts < 0 || experts > n || top <= 0 || top > n || groups <= 0 || n % groups || keep <= 0 || keep > groups)
         return kBadSize;
     if (n > kRouteMax) return kTooLarge;
-    const int grid = (tokens + kRouteWarps - 1) / kRouteWarps;
-    LB_DISPATCH_DTYPE(dtype, moe_route_kernel<T><<<grid, kRouteWarps * 32, 0, (cudaStream_t)stream>>>(
+    LB_DISPATCH_DTYPE(dtype, moe_route_kernel<T><<<tokens, kRouteWarps * 32, 0, (cudaStream_t)stream>>>(
         (const T*)h, w_router, correction, dense, chosen, chosen_w, id_weight, tokens, width, n, experts, top, groups, keep, scale));
     return launch_status();
 }

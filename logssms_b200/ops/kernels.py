@@ -1230,6 +1230,53 @@ def latent_attention(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tenso
     return out
 
 
+LATENT_MMA = os.environ.get("LOGSSMS_B200_LATENT_MMA", "1") != "0"
+
+
+def latent_attention_mma_ok(qa: torch.Tensor, rot: int) -> bool:
+    """Does the tensor-core form take these sizes (else: `latent_attention`)?"""
+    return LATENT_MMA and qa.dtype == torch.bfloat16 and qa.shape[2] % 32 == 0 and qa.shape[2] <= 512 and rot % 16 == 0
+
+
+def latent_splits(num_blocks: int, num_heads: int, keys: int) -> int:
+    """Key ranges per tile so that the grid covers the SMs about twice; a range has at least two 32-key tiles."""
+    ctas = max(1, num_blocks * -(-num_heads // 16))
+    return max(1, min(2 * _SM_COUNT // ctas, -(-keys // 32) // 2, 64))
+
+
+def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
+                         block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, blocks: torch.Tensor | None,
+                         scale: float, window: int = 0, splits: int = 1) -> torch.Tensor:
+    """`latent_attention` on the tensor cores for all tokens of a step.  `blocks`: int32 [n, 2] (first token row, number
+    of tokens) of `StepContext.token_blocks(max(1, 16 // H))`: every token of the step in exactly one block; None: every
+    token a block of its own (a step of single tokens needs no list)."""
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks)
+    T, H, rank = qa.shape
+    rot = kr_cache.shape[-1]
+    _need(latent_attention_mma_ok(qa, rot), "latent_attention_mma takes bfloat16, rank a multiple of 32 up to 512, rot a multiple of 16")
+    _need(qa.is_contiguous() and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
+          "q_rot must be [tokens, H, rot] with unit stride in its last axis")
+    _need(c_cache.dim() == 3 and c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.shape[2] == rank
+          and c_cache.dtype == qa.dtype == kr_cache.dtype and kr_cache.shape[:2] == c_cache.shape[:2], "latent caches do not fit the queries")
+    for t, name in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, name)
+    if blocks is not None:
+        _i32(blocks, "blocks")
+    out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((T * H, splits, rank), dtype=torch.float32, device=qa.device)
+        part_ml = torch.empty((T * H, splits, 2), dtype=torch.float32, device=qa.device)
+    f = _fn("attention_latent", "lb_latent_attention_mma", [c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
+                                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                            c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(qa), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
+             block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), T if blocks is None else blocks.shape[0], _ptr(out), _ptr(part_o),
+             _ptr(part_ml), T, H, rank, rot, c_cache.shape[1], scale, window, splits, _stream()), "latent_attention_mma",
+           f"(rank {rank}, rot {rot})", launches=2 if splits > 1 else 1)
+    return out
+
+
 # --------------------------------------------------------------------------- routed feed-forward
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, num_experts: int, top: int, groups: int,
               keep: int, scale: float):

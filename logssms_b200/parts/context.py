@@ -76,6 +76,16 @@ def chunk_lists(lens, chunk: int, cap_chunks: int | None = None, cap_long: int |
     return _fill(chunks, cap_chunks, (-1, 0), 2), _fill(per_request, cap_long, (-1, 0, 0), 3)
 
 
+def token_block_list(lens, block: int, cap: int | None = None) -> np.ndarray:
+    """int32 [n, 2]: (first token row in the step's batch, number of tokens) for every run of at most `block` neighbouring
+    tokens of one request, all portions alike.  With `cap` the surplus rows name token -1, which the kernels skip."""
+    rows, t = [], 0
+    for n in lens:
+        rows += [(t + o, min(block, int(n) - o)) for o in range(0, int(n), block)]
+        t += int(n)
+    return _fill(rows, cap, (-1, 0), 2)
+
+
 def request_lists(lens, cap_long: int | None = None, cap_short: int | None = None, short_filler: int = 0) -> tuple[np.ndarray, np.ndarray]:
     """(requests with long portions, requests with short ones), int32 indices into the batch."""
     long_r = [b for b, n in enumerate(lens) if n > SHORT_PORTION]
@@ -190,6 +200,13 @@ class StepContext:
         most keys first (a causal tile's cost grows with its position)."""
         cap = None if self.padding is None else -(-self.num_tokens // tile) + self.padding.long_cap
         (t,) = self._lists(("tiles", tile), lambda: (tile_list(self.host_lens, self.host_starts, tile, cap),))
+        return t, t.shape[0]
+
+    def token_blocks(self, block: int) -> tuple[torch.Tensor, int]:
+        """int32 [n, 2] on the device: (first token row, number of tokens) for every run of at most `block` neighbouring
+        tokens of one request (a kernel whose tile holds several tokens of a request takes these as its work list)."""
+        cap = None if self.padding is None else -(-self.num_tokens // block) + self.num_requests
+        (t,) = self._lists(("token_blocks", block), lambda: (token_block_list(self.host_lens, block, cap),))
         return t, t.shape[0]
 
     def fork(self):

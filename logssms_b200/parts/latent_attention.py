@@ -75,7 +75,17 @@ class LatentAttention(Part):
                          self.position.table, self.norm_w, s.norm_eps, c_cache, kr_cache, writes_cache)
         q = proj[:, :H * (s.nope_dim + s.rot_dim)].view(T, H, s.nope_dim + s.rot_dim)
         qa = K.heads_matmul(q[:, :, :s.nope_dim], self.uk)                 # [T, H, rank]
-        lat = K.latent_attention(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
-                                 ctx.positions, s.softmax_scale, s.window or 0)
+        if ctx.host_lens is not None and K.latent_attention_mma_ok(qa, s.rot_dim):
+            # the tensor-core form: tiles of 16 (token, head) rows that share their keys
+            # (a step of single tokens needs no work list: every token is a block of its own)
+            per_block = 1 if ctx.max_len == 1 else max(1, 16 // H)
+            blocks, n_blocks = (None, T) if per_block == 1 else ctx.token_blocks(per_block)
+            keys = min(ctx.max_context, (s.window or ctx.max_context) + per_block)
+            lat = K.latent_attention_mma(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
+                                         ctx.positions, blocks, s.softmax_scale, s.window or 0,
+                                         splits=K.latent_splits(n_blocks, H, keys))
+        else:
+            lat = K.latent_attention(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
+                                     ctx.positions, s.softmax_scale, s.window or 0)
         o = K.heads_matmul(lat, self.uv_t)                                 # [T, H, value]
         return K.linear(o.view(T, H * s.value_dim), self.o_w)

@@ -48,7 +48,7 @@ DUDU_B = _model(96, 333, 1e-6, 1.0, 2.5, 50, 3, 1000003, [
     {**_gla("gla_2", 2, 128, 80, 1.0, 16), "mlp": _moe(24, 1.0, 2, 4, 2, 1, 3, 2.0)},
     {**_latent(4, 32, 32, 32, 8, 72, 1), "mlp": {"kind": "dense", "ff": 50}},
     {**_latent(1, 8, 64, 64, 48, 136, 400, base=1e6), "mlp": None},
-    {**_gla("gla", 5, 8, 8, 64.0, 2), "mlp": {"kind": "dense", "ff": 200}},
+    {**_gla("gla", 5, 8, 24, 64.0, 2), "mlp": {"kind": "dense", "ff": 200}},
 ])
 
 # C: one layer of each mixer with sizes of 1 where the design allows them
