@@ -265,25 +265,67 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
                 const int d = (warp * MT + m) * 16 + g + (e >> 1) * 8, c = col0 + nt * 8 + 2 * t + (e & 1);
                 S[m][nt][e] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
             }
+    // The next chunk's operands travel from global memory to registers while this chunk is computed (16-byte pieces of
+    // q e^{b} and k e^{..}, which are contiguous; v, A and the chunk's decay by plain loads).
+    constexpr int kQK = 4;                                 // 16-byte pieces of a [16][dim] tile per thread: dim <= 256
+    uint4 rq[kQK], rk[kQK];
+    __nv_bfloat16 rv[4];
+    float ra[2], rd[2];
+    const int pieces = dim / 8;                            // per row
+    auto fetch = [&](int ci) {
+        const int t0 = first + ci * kChunk;
+        const int n = min(kChunk, last - t0);
+#pragma unroll
+        for (int u = 0; u < kQK; ++u) {
+            const int i = threadIdx.x + u * 128;
+            rq[u] = rk[u] = make_uint4(0, 0, 0, 0);
+            if (i < kChunk * pieces) {
+                const int j = i / pieces, pc = i % pieces;
+                if (j < n) {
+                    const size_t at = ((size_t)(t0 + j) * H + h) * dim + pc * 8;
+                    rq[u] = *reinterpret_cast<const uint4*>(q_in + at);
+                    rk[u] = *reinterpret_cast<const uint4*>(k_end + at);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = threadIdx.x + u * 128, j = i / kScanCols, c = i % kScanCols;
+            rv[u] = (j < n && col0 + c < vdim) ? v[(size_t)(t0 + j) * v_stride + h * vdim + col0 + c] : __float2bfloat16_rn(0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = threadIdx.x + u * 128, r = i / kChunk;
+            ra[u] = r < n ? A[((size_t)(t0 + r) * H + h) * kChunk + i % kChunk] : 0.f;
+            const int d = threadIdx.x + u * 128;
+            rd[u] = d < dim ? D[((size_t)(chunk0 + ci) * H + h) * dim + d] : 0.f;
+        }
+    };
+    fetch(0);
     for (int ci = 0; ci < nchunks; ++ci) {
         const int t0 = first + ci * kChunk;
         const int n = min(kChunk, last - t0);
         __syncthreads();                                   // the chunk before is done with the shared tiles
-        for (int i = threadIdx.x; i < kChunk * dim; i += blockDim.x) {
-            const int j = i / dim, d = i % dim;
-            const size_t at = ((size_t)(t0 + j) * H + h) * dim + d;
-            Qs[j * DP + d] = j < n ? q_in[at] : __float2bfloat16_rn(0.f);
-            Ks[j * DP + d] = j < n ? k_end[at] : __float2bfloat16_rn(0.f);
+#pragma unroll
+        for (int u = 0; u < kQK; ++u) {
+            const int i = threadIdx.x + u * 128;
+            if (i < kChunk * pieces) {
+                const int j = i / pieces, pc = i % pieces;
+                *reinterpret_cast<uint4*>(Qs + j * DP + pc * 8) = rq[u];
+                *reinterpret_cast<uint4*>(Ks + j * DP + pc * 8) = rk[u];
+            }
         }
-        for (int i = threadIdx.x; i < kChunk * kScanCols; i += blockDim.x) {
-            const int j = i / kScanCols, c = i % kScanCols;
-            Vs[j * VP + c] = (j < n && col0 + c < vdim) ? v[(size_t)(t0 + j) * v_stride + h * vdim + col0 + c] : __float2bfloat16_rn(0.f);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = threadIdx.x + u * 128;
+            Vs[(i / kScanCols) * VP + i % kScanCols] = rv[u];
         }
-        for (int i = threadIdx.x; i < kChunk * kChunk; i += blockDim.x) {
-            const int r = i / kChunk;
-            As[i] = r < n ? A[((size_t)(t0 + r) * H + h) * kChunk + i % kChunk] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            As[threadIdx.x + u * 128] = ra[u];
+            if (threadIdx.x + u * 128 < dim) Ds[threadIdx.x + u * 128] = rd[u];
         }
-        for (int d = threadIdx.x; d < dim; d += blockDim.x) Ds[d] = D[((size_t)(chunk0 + ci) * H + h) * dim + d];
+        if (ci + 1 < nchunks) fetch(ci + 1);
         // the state as it stands before this chunk, rounded, as the operand of the output product
 #pragma unroll
         for (int m = 0; m < MT; ++m) {

@@ -100,4 +100,6 @@ def row_errors(got: torch.Tensor, want: torch.Tensor) -> torch.Tensor:
     return d.pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-30)
 
 
-TOL = {"float32": 1e-4, "bfloat16": 5e-2}
+# (tiny random models are ill-conditioned at their first positions: a head norm over one or two nearly cancelling outer
+# products multiplies float32 rounding a hundredfold; a wrong or missing term moves the logits by tenths)
+TOL = {"float32": 3e-4, "bfloat16": 5e-2}
