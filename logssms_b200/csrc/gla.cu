@@ -215,9 +215,10 @@ __global__ void __launch_bounds__(128) gla_chunk_prepare_kernel(
     for (int p = warp; p < n * kChunk; p += nwarps) {
         const int i = p / kChunk, j = p % kChunk;
         float a = 0.f;
-        if (j <= i)
-            for (int d = lane; d < dim; d += 32) a += qs[i * dim + d] * ks[j * dim + d] * expf(b[i * dim + d] - b[j * dim + d]);
-        a = warp_sum(a);
+        if (j <= i) {
+            for (int d = lane; d < dim; d += 32) a += qs[i * dim + d] * ks[j * dim + d] * __expf(b[i * dim + d] - b[j * dim + d]);
+            a = warp_sum(a);
+        }
         if (lane == 0) A[((size_t)(t0 + i) * H + h) * kChunk + j] = a;
     }
 }
@@ -231,13 +232,19 @@ __device__ __forceinline__ uint32_t pack2(__nv_bfloat16 lo, __nv_bfloat16 hi) {
     return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
 
-// grid (ceil(vdim / 32), H, long requests); 4 warps; MT: 16-row state tiles per warp (dim <= 64 * MT)
-template <int MT>
+// grid (ceil(vdim / 32), H, work items); 4 warps; MT: 16-row state tiles per warp (dim <= 64 * MT).
+// MODE 0: an item is a request (request, first chunk, chunks): from its slot's state to its slot's state, writing o.
+// A lone long prompt has too few such items to fill the GPU, so it may run in segments of chunks instead, an item
+// being (request, first chunk, chunks, first token within the portion):
+// MODE 1: a segment from a zero state, no output: leaves its end state in seg_state[item] and the product of its
+//         chunks' decays in seg_decay[item]; `gla_segment_pass` then turns the end states into start states;
+// MODE 2: a segment from seg_state[item], writing o.
+template <int MT, int MODE>
 __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
         const __nv_bfloat16* __restrict__ q_in, const __nv_bfloat16* __restrict__ k_end, const __nv_bfloat16* __restrict__ v,
         long v_stride, const float* __restrict__ A, const float* __restrict__ D, float* __restrict__ o, float* state,
         const int* __restrict__ cu, const int* __restrict__ start_pos, const int* __restrict__ slots,
-        const int* __restrict__ per_request, int H, int dim, int vdim) {
+        const int* __restrict__ per_request, int H, int dim, int vdim, float* seg_state, float* seg_decay) {
     constexpr int NT = kScanCols / 8;
     extern __shared__ __align__(16) unsigned char raw[];
     const int DP = dim + 8, VP = kScanCols + 8;
@@ -247,14 +254,20 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
     __nv_bfloat16* Vs = Sb + dim * VP;                                   // [16][VP]
     float* As = reinterpret_cast<float*>(Vs + kChunk * VP);              // [16][16]
     float* Ds = As + kChunk * kChunk;                                    // [dim]
-    const int req = per_request[3 * blockIdx.z];
+    constexpr int W = MODE == 0 ? 3 : 4;
+    const int req = per_request[W * blockIdx.z];
     if (req < 0) return;
-    const int chunk0 = per_request[3 * blockIdx.z + 1], nchunks = per_request[3 * blockIdx.z + 2];
+    const int chunk0 = per_request[W * blockIdx.z + 1], nchunks = per_request[W * blockIdx.z + 2];
     const int h = blockIdx.y, col0 = blockIdx.x * kScanCols;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int first = cu[req], last = cu[req + 1];
-    const size_t sbase = ((size_t)slots[req] * H + h) * dim * vdim;
-    const bool fresh = start_pos[req] == 0;
+    const int first = cu[req] + (MODE == 0 ? 0 : per_request[W * blockIdx.z + 3]), last = cu[req + 1];
+    // where the state comes from and goes to: the request's slot, or the segment's entry of the scratch
+    float* sfrom = MODE == 0 ? state + ((size_t)slots[req] * H + h) * dim * vdim
+                             : seg_state + ((size_t)blockIdx.z * H + h) * dim * vdim;
+    const bool fresh = MODE == 1 || (MODE == 0 && start_pos[req] == 0);
+    float* state_ = sfrom;
+    const size_t sbase = 0;
+    float pd[2] = {1.f, 1.f};                               // MODE 1: the product of the chunks' decays
     float S[MT][NT][4];
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -263,7 +276,7 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int d = (warp * MT + m) * 16 + g + (e >> 1) * 8, c = col0 + nt * 8 + 2 * t + (e & 1);
-                S[m][nt][e] = (!fresh && d < dim && c < vdim) ? state[sbase + (size_t)d * vdim + c] : 0.f;
+                S[m][nt][e] = (!fresh && d < dim && c < vdim) ? state_[sbase + (size_t)d * vdim + c] : 0.f;
             }
     // The next chunk's operands travel from global memory to registers while this chunk is computed (16-byte pieces of
     // q e^{b} and k e^{..}, which are contiguous; v, A and the chunk's decay by plain loads).
@@ -323,14 +336,14 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             As[threadIdx.x + u * 128] = ra[u];
-            if (threadIdx.x + u * 128 < dim) Ds[threadIdx.x + u * 128] = rd[u];
+            if (threadIdx.x + u * 128 < dim) { Ds[threadIdx.x + u * 128] = rd[u]; pd[u] *= rd[u]; }
         }
         if (ci + 1 < nchunks) fetch(ci + 1);
         // the state as it stands before this chunk, rounded, as the operand of the output product
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             const int r0 = (warp * MT + m) * 16 + g;
-            if (r0 - g < dim) {
+            if (MODE != 1 && r0 - g < dim) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const int c = nt * 8 + 2 * t;
@@ -341,7 +354,7 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
         }
         __syncthreads();
         // o[16 tokens][8 columns of this warp] = Qs Sb + As Vs
-        {
+        if (MODE != 1) {
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             const int cw = warp * 8;
             for (int kk = 0; kk < dim; kk += 16) {
@@ -390,8 +403,37 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int d = (warp * MT + m) * 16 + g + (e >> 1) * 8, c = col0 + nt * 8 + 2 * t + (e & 1);
-                if (d < dim && c < vdim) state[sbase + (size_t)d * vdim + c] = S[m][nt][e];
+                if (MODE != 2 && d < dim && c < vdim) state_[sbase + (size_t)d * vdim + c] = S[m][nt][e];
             }
+    if (MODE == 1 && blockIdx.x == 0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            if (threadIdx.x + u * 128 < dim) seg_decay[((size_t)blockIdx.z * H + h) * dim + threadIdx.x + u * 128] = pd[u];
+    }
+}
+
+// Between the two passes over segments: start states from end states.  per_request: int32 [m, 3] (request, its first
+// segment, its segments).  For every state element: s = the slot's state (0 for a request that starts at position 0);
+// for each segment: swap(seg_state[segment], s) and s = seg_decay[segment] * s_before + end state; at last the slot's
+// state = s.  grid (ceil(dim * vdim / 256), H, requests)
+__global__ void gla_segment_pass_kernel(float* seg_state, const float* __restrict__ seg_decay, float* state,
+                                        const int* __restrict__ start_pos, const int* __restrict__ slots,
+                                        const int* __restrict__ per_request, int H, int dim, int vdim) {
+    const int req = per_request[3 * blockIdx.z];
+    if (req < 0) return;
+    const int seg0 = per_request[3 * blockIdx.z + 1], nseg = per_request[3 * blockIdx.z + 2];
+    const int h = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= dim * vdim) return;
+    const int d = i / vdim;
+    float* slot = state + ((size_t)slots[req] * H + h) * dim * vdim + i;
+    float s = start_pos[req] == 0 ? 0.f : *slot;
+    for (int g = seg0; g < seg0 + nseg; ++g) {
+        float* e = seg_state + ((size_t)g * H + h) * dim * vdim + i;
+        const float end = *e;
+        *e = s;
+        s = seg_decay[((size_t)g * H + h) * dim + d] * s + end;
+    }
+    *slot = s;
 }
 
 // Chunked form over the long portions of a step (bfloat16).  q, k, v: column views of one projection buffer; z as for
@@ -401,7 +443,8 @@ __global__ void __launch_bounds__(128) gla_chunk_scan_kernel(
 extern "C" int lb_gla_chunked(const void* q, const void* k, const void* v, long row_stride, const float* z, float* o, float* state,
                               const int* cu, const int* start_pos, const int* slots, const int* chunks, int num_chunks,
                               const int* per_request, int num_long, void* q_in, void* k_end, float* A, float* D, int H, int dim,
-                              int vdim, float tau, float q_scale, void* stream) {
+                              int vdim, float tau, float q_scale, const int* segments, int num_segments, float* seg_state,
+                              float* seg_decay, void* stream) {
     if (num_chunks <= 0 || num_long <= 0) return kOk;
     if (H <= 0 || dim <= 0 || vdim <= 0 || !(tau > 0.f) || dim % 16) return kBadSize;
     if (dim > 256) return kTooLarge;
@@ -419,10 +462,25 @@ extern "C" int lb_gla_chunked(const void* q, const void* k, const void* v, long 
     const size_t smem = ((size_t)2 * kChunk * (dim + 8) + (size_t)dim * (kScanCols + 8) + (size_t)kChunk * (kScanCols + 8)) * sizeof(bf)
                         + ((size_t)kChunk * kChunk + dim) * sizeof(float);
     dim3 grid((vdim + kScanCols - 1) / kScanCols, H, num_long);
-#define LB_SCAN(MT_) { static size_t have = 0; ensure_dynamic_smem(gla_chunk_scan_kernel<MT_>, smem, have); \
-        gla_chunk_scan_kernel<MT_><<<grid, 128, smem, st>>>((const bf*)q_in, (const bf*)k_end, (const bf*)v, row_stride, A, D, o, state, \
-                                                           cu, start_pos, slots, per_request, H, dim, vdim); }
-    if (dim <= 64) LB_SCAN(1) else if (dim <= 128) LB_SCAN(2) else LB_SCAN(4)
+#define LB_SCAN(MT_, MODE_, LIST_) { static size_t have = 0; ensure_dynamic_smem(gla_chunk_scan_kernel<MT_, MODE_>, smem, have); \
+        gla_chunk_scan_kernel<MT_, MODE_><<<grid, 128, smem, st>>>((const bf*)q_in, (const bf*)k_end, (const bf*)v, row_stride, A, D, o, \
+            state, cu, start_pos, slots, LIST_, H, dim, vdim, seg_state, seg_decay); }
+#define LB_SCAN_MODE(MODE_, LIST_) { if (dim <= 64) LB_SCAN(1, MODE_, LIST_) else if (dim <= 128) LB_SCAN(2, MODE_, LIST_) else LB_SCAN(4, MODE_, LIST_) }
+    if (segments == nullptr || num_segments <= 0) {
+        LB_SCAN_MODE(0, per_request)
+        return launch_status();
+    }
+    // a lone long prompt: its segments side by side, twice, with the pass over their states between
+    grid.z = num_segments;
+    LB_SCAN_MODE(1, segments)
+    int rc = launch_status();
+    if (rc != 0) return rc;
+    gla_segment_pass_kernel<<<dim3((dim * vdim + 255) / 256, H, num_long), 256, 0, st>>>(seg_state, seg_decay, state, start_pos, slots,
+                                                                                        per_request, H, dim, vdim);
+    rc = launch_status();
+    if (rc != 0) return rc;
+    LB_SCAN_MODE(2, segments)
+#undef LB_SCAN_MODE
 #undef LB_SCAN
     return launch_status();
 }

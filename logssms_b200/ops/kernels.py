@@ -1111,10 +1111,13 @@ def gla_chunked_ok(qkv: torch.Tensor, key_dim: int) -> bool:
 
 def gla_chunked(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
                 slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int, per_request: torch.Tensor, num_long: int,
-                num_heads: int, key_dim: int, value_dim: int, tau: float, q_scale: float, out: torch.Tensor) -> torch.Tensor:
+                num_heads: int, key_dim: int, value_dim: int, tau: float, q_scale: float, out: torch.Tensor,
+                segments: torch.Tensor | None = None, segment_requests: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence of `gla_scan` over the long portions of a step in chunks of `GLA_CHUNK` tokens on the tensor cores
     (see `csrc/gla.cu`); the rows of the other requests in `out` (float32 [tokens, H*value_dim]) are left alone.
-    `chunks`, `per_request`: the work lists of `StepContext.long_portion_chunks(GLA_CHUNK)`."""
+    `chunks`, `per_request`: the work lists of `StepContext.long_portion_chunks(GLA_CHUNK)`.  With `segments` and
+    `segment_requests` (`StepContext.long_portion_segments`) every request's segments run side by side, twice, with a
+    pass over their states between: for steps whose few long portions would leave most of the GPU idle."""
     _cuda(qkv, z, state, cu_seqlens, start_pos, slots, chunks, per_request, out)
     H, dk, dv = num_heads, key_dim, value_dim
     T = qkv.shape[0]
@@ -1130,15 +1133,34 @@ def gla_chunked(qkv: torch.Tensor, z: torch.Tensor, state: torch.Tensor, cu_seql
     k_end = torch.empty((T, H, dk), dtype=torch.bfloat16, device=qkv.device)
     A = torch.empty((T, H, GLA_CHUNK), dtype=torch.float32, device=qkv.device)
     D = torch.empty((max(num_chunks, 1), H, dk), dtype=torch.float32, device=qkv.device)
+    seg_state = seg_decay = None
+    n_seg = 0
+    if segments is not None:
+        _need(segment_requests is not None, "segments come with their per-request list")
+        _i32(segments, "segments")
+        _i32(segment_requests, "segment_requests")
+        n_seg = segments.shape[0]
+        seg_state = torch.empty((max(n_seg, 1), H, dk, dv), dtype=torch.float32, device=qkv.device)
+        seg_decay = torch.empty((max(n_seg, 1), H, dk), dtype=torch.float32, device=qkv.device)
+        per_request, num_long = segment_requests, segment_requests.shape[0]
     item, base = qkv.element_size(), qkv.data_ptr()
     f = _fn("gla", "lb_gla_chunked", [c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                      c_float, c_float, c_void_p])
+                                      c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(base, base + H * dk * item, base + 2 * H * dk * item, qkv.stride(0) if T > 1 else qkv.shape[1], _ptr(z), _ptr(out),
              _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots), _ptr(chunks), num_chunks, _ptr(per_request), num_long,
-             _ptr(q_in), _ptr(k_end), _ptr(A), _ptr(D), H, dk, dv, tau, q_scale, _stream()), "gla_chunked",
-           f"(key_dim {dk}, value_dim {dv})", launches=2)
+             _ptr(q_in), _ptr(k_end), _ptr(A), _ptr(D), H, dk, dv, tau, q_scale, _ptr(segments), n_seg, _ptr(seg_state),
+             _ptr(seg_decay), _stream()), "gla_chunked", f"(key_dim {dk}, value_dim {dv})", launches=2 if segments is None else 4)
     return out
+
+
+GLA_SEGMENT = 16      # chunks per segment of the side-by-side form
+
+
+def gla_segmented_pays(num_tokens: int, num_long: int, num_heads: int, value_dim: int) -> bool:
+    """Should the long portions of a step run as segments side by side?  When one CTA per (request, head, 32 value
+    columns) would leave most SMs idle and the portions are long enough to be cut."""
+    return num_tokens >= 2 * GLA_SEGMENT * GLA_CHUNK and num_long * num_heads * -(-value_dim // 32) < _SM_COUNT
 
 
 def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, num_heads: int) -> torch.Tensor:

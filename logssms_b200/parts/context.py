@@ -76,6 +76,21 @@ def chunk_lists(lens, chunk: int, cap_chunks: int | None = None, cap_long: int |
     return _fill(chunks, cap_chunks, (-1, 0), 2), _fill(per_request, cap_long, (-1, 0, 0), 3)
 
 
+def segment_lists(lens, chunk: int, per_segment: int, cap_segments: int | None = None, cap_long: int | None = None):
+    """Work lists of a chunked scan that walks the segments of a long portion side by side: int32 [n, 4] (request index,
+    the segment's first chunk in the order of `chunk_lists`, its number of chunks, its first token within the portion)
+    and int32 [m, 3] (request index, its first segment, its number of segments).  Surplus rows name request -1."""
+    segments, per_request, chunk_at = [], [], 0
+    for b, n in enumerate(lens):
+        if n > SHORT_PORTION:
+            chunks = -(-int(n) // chunk)
+            first = len(segments)
+            segments += [(b, chunk_at + c0, min(per_segment, chunks - c0), c0 * chunk) for c0 in range(0, chunks, per_segment)]
+            per_request.append((b, first, len(segments) - first))
+            chunk_at += chunks
+    return _fill(segments, cap_segments, (-1, 0, 0, 0), 4), _fill(per_request, cap_long, (-1, 0, 0), 3)
+
+
 def token_block_list(lens, block: int, cap: int | None = None) -> np.ndarray:
     """int32 [n, 2]: (first token row in the step's batch, number of tokens) for every run of at most `block` neighbouring
     tokens of one request, all portions alike.  With `cap` the surplus rows name token -1, which the kernels skip."""
@@ -253,6 +268,16 @@ class StepContext:
             caps = (-(-self.num_tokens // chunk) + self.padding.long_cap, self.padding.long_cap)
         c, r = self._lists(("chunks", chunk), lambda: chunk_lists(self.host_lens, chunk, *caps))
         return c, c.shape[0], r, r.shape[0]
+
+    def long_portion_segments(self, chunk: int, per_segment: int) -> tuple[torch.Tensor, int, torch.Tensor, int]:
+        """Work lists of a chunked scan over segments of `per_segment` chunks (see `segment_lists`), with their counts."""
+        if self.padding is None:
+            caps = (None, None)
+        else:
+            chunks = -(-self.num_tokens // chunk) + self.padding.long_cap
+            caps = (-(-chunks // per_segment) + self.padding.long_cap, self.padding.long_cap)
+        g, r = self._lists(("segments", chunk, per_segment), lambda: segment_lists(self.host_lens, chunk, per_segment, *caps))
+        return g, g.shape[0], r, r.shape[0]
 
     def requests_by_portion(self) -> tuple[torch.Tensor, int, torch.Tensor, int]:
         """(long request indices, their count, short request indices, their count), int32 on the device."""

@@ -72,8 +72,13 @@ class GatedLinearAttention(Part):
             chunks, n_chunks, per_request, n_long = ctx.long_portion_chunks(K.GLA_CHUNK)
             _, _, short_list, n_short = ctx.requests_by_portion()
             o = torch.empty((x.shape[0], vg), dtype=torch.float32, device=x.device)
+            seg = {}
+            if K.gla_segmented_pays(ctx.num_tokens, n_long, s.num_heads, s.value_dim):
+                # few long portions (a lone prompt): their segments side by side instead of one CTA walking each
+                segments, _, seg_requests, _ = ctx.long_portion_segments(K.GLA_CHUNK, K.GLA_SEGMENT)
+                seg = {"segments": segments, "segment_requests": seg_requests}
             K.gla_chunked(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, chunks, n_chunks, per_request, n_long,
-                          *sizes, out=o)
+                          *sizes, out=o, **seg)
             if n_short > 0:
                 K.gla_scan(proj, z, state, ctx.cu_seqlens, ctx.start_pos, ctx.slots, ctx.num_requests, *sizes,
                            request_list=short_list, out=o)

@@ -110,6 +110,25 @@ def test_gated_linear_attention_in_portions(dtype, heads, dim, vdim, tau, rank):
             close(y, P.gla(x.double(), w, {}, heads=heads, dim=dim, vdim=vdim, tau=tau, eps=1e-5), dtype)
 
 
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 64, 72), (1, 144, 32)])
+def test_a_lone_long_prompt_runs_its_segments_side_by_side(heads, dim, vdim):
+    """Few long portions: the chunked form cuts them into segments that run side by side with a pass over their states
+    between (bfloat16).  Two requests, cut so that a later portion starts from the state the segments left."""
+    from logssms_b200.config.specs import GLASpec
+    from logssms_b200.ops import kernels as K
+    from logssms_b200.parts import GatedLinearAttention
+    dtype = torch.bfloat16
+    assert K.gla_segmented_pays(600, 2, heads, vdim)
+    part = GatedLinearAttention(GLASpec(56, heads, dim, vdim, 8.0, 1e-5, 4), perturb_init=True)
+    w = f64(give_weights(part, dtype, seed=3))
+    cache, planner = cache_for([part.cache_needs()], dtype, max_requests=2, max_seq_len=2048)
+    lengths = [1100, 700]
+    xs = inputs(lengths, 56, dtype, seed=4)
+    got = step_in_portions(planner, cache, lengths, [[530, 0], [3, 690], [567, 10]], lambda ctx, spans: part.forward(rows_of(xs, spans), ctx, 0))
+    for x, y in zip(xs, got):
+        close(y, P.gla(x.double(), w, {}, heads=heads, dim=dim, vdim=vdim, tau=8.0, eps=1e-5), dtype)
+
+
 def test_gated_linear_attention_remembers_a_token_hundreds_of_steps_back():
     """Decays of nearly one: the first token's key/value pair is still most of the state 600 tokens later, through
     prompt portions and single decoded tokens; a state that is lost or started anew anywhere changes every later row."""

@@ -87,8 +87,8 @@ def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
         bad = err > TOL[dtype]
         # float32: no position may differ.  bfloat16 against a float64 oracle: a position where the model itself is
         # ill-conditioned (a head norm over a few nearly cancelling values) may be off by more than rounding elsewhere;
-        # one in twenty-five may, by at most four times the tolerance
-        allowed = 0 if dtype == "float32" else max(1, len(err) // 25)
+        # a few may (two, or one in sixteen), by at most four times the tolerance
+        allowed = 0 if dtype == "float32" else max(2, len(err) // 16)
         assert int(bad.sum()) <= allowed and float(err.max()) <= (1 if dtype == "float32" else 4) * TOL[dtype], \
             f"{name} {dtype} {u}: error {float(err.max()):.3g}, {int(bad.sum())} positions over {TOL[dtype]}; first bad " \
             f"position {int(bad.nonzero()[0])}"
