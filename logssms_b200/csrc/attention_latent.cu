@@ -68,12 +68,15 @@ extern "C" int lb_latent_prepare(void* proj, long row_stride, int q_cols, int H,
     return launch_status();
 }
 
-// grid (ceil(N / 128), H, ceil(tokens / 8)); a[t*a_row + h*a_head + k]; w [H, K, N]; out[t*o_row + h*o_head + n]
+// grid (ceil(N / 32), H, ceil(tokens / 8)), 128 threads: 32 output columns x 4 slices of K, summed through shared
+// memory (a step of few tokens then still has enough CTAs in flight to stream the weights);
+// a[t*a_row + h*a_head + k]; w [H, K, N]; out[t*o_row + h*o_head + n]
 constexpr int kHmTokens = 8;
 template <typename T>
-__global__ void heads_matmul_kernel(const T* __restrict__ a, long a_row, long a_head, const T* __restrict__ w,
-                                    T* __restrict__ out, long o_row, long o_head, int tokens, int K, int N) {
-    extern __shared__ float as[];                    // [kHmTokens][K]
+__global__ void __launch_bounds__(128) heads_matmul_kernel(const T* __restrict__ a, long a_row, long a_head, const T* __restrict__ w,
+                                                           T* __restrict__ out, long o_row, long o_head, int tokens, int K, int N) {
+    extern __shared__ float as[];                    // [kHmTokens][K], then [4][kHmTokens][32] partial sums
+    float* part = as + kHmTokens * K;
     const int h = blockIdx.y, t0 = blockIdx.z * kHmTokens;
     const int nt = min(kHmTokens, tokens - t0);
     for (int i = threadIdx.x; i < kHmTokens * K; i += blockDim.x) {
@@ -81,27 +84,40 @@ __global__ void heads_matmul_kernel(const T* __restrict__ a, long a_row, long a_
         as[i] = tt < nt ? to_f32(a[(size_t)(t0 + tt) * a_row + (size_t)h * a_head + kk]) : 0.f;
     }
     __syncthreads();
-    const int n = blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= N) return;
+    const int col = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int n = blockIdx.x * 32 + col;
     float acc[kHmTokens];
 #pragma unroll
     for (int tt = 0; tt < kHmTokens; ++tt) acc[tt] = 0.f;
-    const T* wp = w + (size_t)h * K * N + n;
-    for (int kk = 0; kk < K; ++kk) {
-        const float wv = to_f32(wp[(size_t)kk * N]);
+    if (n < N) {
+        const T* wp = w + (size_t)h * K * N + n;
+#pragma unroll 4
+        for (int kk = slice; kk < K; kk += 4) {
+            const float wv = to_f32(wp[(size_t)kk * N]);
 #pragma unroll
-        for (int tt = 0; tt < kHmTokens; ++tt) acc[tt] += as[tt * K + kk] * wv;
+            for (int tt = 0; tt < kHmTokens; ++tt) acc[tt] += as[tt * K + kk] * wv;
+        }
     }
-    for (int tt = 0; tt < nt; ++tt) out[(size_t)(t0 + tt) * o_row + (size_t)h * o_head + n] = from_f32<T>(acc[tt]);
+#pragma unroll
+    for (int tt = 0; tt < kHmTokens; ++tt) part[(slice * kHmTokens + tt) * 32 + col] = acc[tt];
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+        const int tt = i >> 5, c = i & 31, nn = blockIdx.x * 32 + c;
+        if (nn < N) {
+            const float sum = (part[tt * 32 + c] + part[(kHmTokens + tt) * 32 + c])
+                            + (part[(2 * kHmTokens + tt) * 32 + c] + part[(3 * kHmTokens + tt) * 32 + c]);
+            out[(size_t)(t0 + tt) * o_row + (size_t)h * o_head + nn] = from_f32<T>(sum);
+        }
+    }
 }
 
 extern "C" int lb_heads_matmul(const void* a, long a_row, long a_head, const void* w, void* out, long o_row, long o_head,
                                int tokens, int H, int K, int N, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (H <= 0 || K <= 0 || N <= 0) return kBadSize;
-    const size_t smem = (size_t)kHmTokens * K * sizeof(float);
+    const size_t smem = ((size_t)kHmTokens * K + 4 * kHmTokens * 32) * sizeof(float);
     if (smem > 160 * 1024) return kTooLarge;
-    dim3 grid((N + 127) / 128, H, (tokens + kHmTokens - 1) / kHmTokens);
+    dim3 grid((N + 31) / 32, H, (tokens + kHmTokens - 1) / kHmTokens);
     LB_DISPATCH_DTYPE(dtype, {
         static size_t have = 0;
         ensure_dynamic_smem(heads_matmul_kernel<T>, smem, have);
@@ -225,6 +241,10 @@ __device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
     return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
@@ -232,8 +252,8 @@ __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi
 // grid (token blocks, head groups, splits); NTW: 8-column output tiles per warp (rank <= 32 * NTW)
 template <int NTW>
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
-        const __nv_bfloat16* __restrict__ qa, const __nv_bfloat16* __restrict__ q_rot, long q_rot_row, long q_rot_head,
-        const __nv_bfloat16* __restrict__ c_cache, const __nv_bfloat16* __restrict__ kr_cache,
+        const __nv_bfloat16* __restrict__ qa, long qa_row, long qa_head, const __nv_bfloat16* __restrict__ q_rot, long q_rot_row,
+        long q_rot_head, const __nv_bfloat16* __restrict__ c_cache, const __nv_bfloat16* __restrict__ kr_cache,
         const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
         const int* __restrict__ positions, const int* __restrict__ blocks, __nv_bfloat16* __restrict__ out,
         float* __restrict__ part_o, float* __restrict__ part_ml, int H, int rank, int rot, int page_size, float scale,
@@ -242,8 +262,8 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     extern __shared__ __align__(16) unsigned char raw[];
     const int D = rank + rot, DP = D + 8, PP = kMmaKeys + 8;
     bf* Qs = reinterpret_cast<bf*>(raw);                    // [16][DP]
-    bf* Kt = Qs + 16 * DP;                                  // [32][DP]
-    bf* Ps = Kt + kMmaKeys * DP;                            // [16][PP]
+    bf* Kt0 = Qs + 16 * DP;                                 // two buffers of [32][DP]
+    bf* Ps = Kt0 + 2 * kMmaKeys * DP;                       // [16][PP]
     float* red = reinterpret_cast<float*>(Ps + 16 * PP);    // [4][16]
     __shared__ int row_lo[16], row_hi[16];
     const int t0 = blocks ? blocks[2 * blockIdx.x] : blockIdx.x, ntok = blocks ? blocks[2 * blockIdx.x + 1] : 1;
@@ -265,7 +285,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         const int r = i / D, d = i % D, tok = r / nh, h = h0 + r % nh;
         bf v = __float2bfloat16_rn(0.f);
         if (tok < ntok)
-            v = d < rank ? qa[((size_t)(t0 + tok) * H + h) * rank + d]
+            v = d < rank ? qa[(size_t)(t0 + tok) * qa_row + (size_t)h * qa_head + d]
                          : q_rot[(size_t)(t0 + tok) * q_rot_row + (size_t)h * q_rot_head + d - rank];
         Qs[r * DP + d] = v;
     }
@@ -282,23 +302,31 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     const int colw = warp * (rank / 4);
     __syncthreads();
     const int lo0 = row_lo[g], hi0 = row_hi[g], lo1 = row_lo[g + 8], hi1 = row_hi[g + 8];
-    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    // key tiles come by 16-byte asynchronous copies into two buffers: the next tile travels while this one is used
+    auto stage = [&](int tile, bf* dstbase) {
         const int j0 = key_lo + tile * kMmaKeys;
-        __syncthreads();                                     // the tile before is used up
         for (int jj = warp; jj < kMmaKeys; jj += 4) {
             const int j = j0 + jj;
-            uint4* dst = reinterpret_cast<uint4*>(Kt + jj * DP);
+            bf* dst = dstbase + jj * DP;
             if (j <= p_hi) {
                 const size_t off = (size_t)pages[j / page_size] * page_size + j % page_size;
-                const uint4* c4 = reinterpret_cast<const uint4*>(c_cache + off * rank);
-                const uint4* k4 = reinterpret_cast<const uint4*>(kr_cache + off * rot);
-                for (int i = lane; i < rank / 8; i += 32) dst[i] = c4[i];
-                for (int i = lane; i < rot / 8; i += 32) dst[rank / 8 + i] = k4[i];
+                const bf* c4 = c_cache + off * rank;
+                const bf* k4 = kr_cache + off * rot;
+                for (int i = lane; i < rank / 8; i += 32) cp_async_16(dst + i * 8, c4 + i * 8);
+                for (int i = lane; i < rot / 8; i += 32) cp_async_16(dst + rank + i * 8, k4 + i * 8);
             } else {
-                for (int i = lane; i < D / 8; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+                for (int i = lane; i < D / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
             }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (tile_lo < tile_hi) stage(tile_lo, Kt0);
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+        const int j0 = key_lo + tile * kMmaKeys;
+        bf* Kt = Kt0 + ((tile - tile_lo) & 1) * kMmaKeys * DP;
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();                                     // this tile has landed; the tile before is used up
+        if (tile + 1 < tile_hi) stage(tile + 1, Kt0 + ((tile + 1 - tile_lo) & 1) * kMmaKeys * DP);
         // scores of this warp's 8 keys
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const bf* kb = Kt + (warp * 8 + g) * DP;
@@ -417,7 +445,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
 // or null: every token a block of its own (num_blocks = tokens).
 // Every token of the step lies in exactly one block.  part_o float32 [tokens * H, splits, rank] and part_ml float32
 // [tokens * H, splits, 2]: scratch for splits > 1 (every row is written by the CTAs of its block).
-extern "C" int lb_latent_attention_mma(const void* qa, const void* q_rot, long q_rot_row, long q_rot_head, const void* c_cache,
+extern "C" int lb_latent_attention_mma(const void* qa, long qa_row, long qa_head, const void* q_rot, long q_rot_row, long q_rot_head, const void* c_cache,
                                        const void* kr_cache, const int* block_table, int table_width, const int* token_req,
                                        const int* positions, const int* blocks, int num_blocks, void* out, float* part_o,
                                        float* part_ml, int tokens, int H, int rank, int rot, int page_size, float scale,
@@ -427,11 +455,11 @@ extern "C" int lb_latent_attention_mma(const void* qa, const void* q_rot, long q
     if (rank > 512 || splits > 65535) return kTooLarge;
     typedef __nv_bfloat16 bf;
     const int D = rank + rot;
-    const size_t smem = ((size_t)(16 + kMmaKeys) * (D + 8) + 16 * (kMmaKeys + 8)) * sizeof(bf) + 64 * sizeof(float);
+    const size_t smem = ((size_t)(16 + 2 * kMmaKeys) * (D + 8) + 16 * (kMmaKeys + 8)) * sizeof(bf) + 64 * sizeof(float);
     dim3 grid(num_blocks, H >= 16 ? (H + 15) / 16 : 1, splits);
     cudaStream_t st = (cudaStream_t)stream;
 #define LB_LA(NTW_) { static size_t have = 0; ensure_dynamic_smem(latent_attention_mma_kernel<NTW_>, smem, have); \
-        latent_attention_mma_kernel<NTW_><<<grid, 128, smem, st>>>((const bf*)qa, (const bf*)q_rot, q_rot_row, q_rot_head, \
+        latent_attention_mma_kernel<NTW_><<<grid, 128, smem, st>>>((const bf*)qa, qa_row, qa_head, (const bf*)q_rot, q_rot_row, q_rot_head, \
             (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, part_o, \
             part_ml, H, rank, rot, page_size, scale, window, splits); }
     if (rank <= 128) LB_LA(4) else if (rank <= 256) LB_LA(8) else LB_LA(16)

@@ -15,7 +15,7 @@
 using namespace lb200;
 
 constexpr int kRouteMax = 256;        // router outputs
-constexpr int kRouteWarps = 4;        // warps of a token's CTA: each takes every fourth router output
+constexpr int kRouteWarps = 8;        // warps of a token's CTA: each takes every eighth router output
 
 // grid (tokens)
 template <typename T>
@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
         const float* wr = w_router + (size_t)e * width;
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         int k = lane;
+#pragma unroll 2
         for (; k + 96 < width; k += 128) {
             a0 += to_f32(hr[k]) * wr[k];
             a1 += to_f32(hr[k + 32]) * wr[k + 32];
@@ -124,10 +125,46 @@ __global__ void moe_activation_kernel(const T* __restrict__ gu, const float* __r
     y[(t * experts + e) * (size_t)ff + i] = from_f32<T>(v);
 }
 
+// the same for bfloat16 rows with ff a multiple of 8: a CTA per token walks its experts' rows in 16-byte pieces, and writes
+// zeros for the experts that were not chosen without reading their products
+__global__ void __launch_bounds__(256) moe_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ dense,
+                                                                 __nv_bfloat16* __restrict__ y, int experts, int ff, int n,
+                                                                 float limit, float act_alpha) {
+    const size_t t = blockIdx.x;
+    const int pieces = ff / 8;
+    for (int i = threadIdx.x; i < experts * pieces; i += blockDim.x) {
+        const int e = i / pieces, pc = i % pieces;
+        const float w = dense[t * n + e];
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (w != 0.f) {
+            const __nv_bfloat16* row = gu + (t * experts + e) * 2 * (size_t)ff;
+            const uint4 gv = *reinterpret_cast<const uint4*>(row + pc * 8);
+            const uint4 uv = *reinterpret_cast<const uint4*>(row + ff + pc * 8);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+                const float g0 = fminf(g.x, limit), g1 = fminf(g.y, limit);
+                const float u0 = fminf(fmaxf(u.x, -limit), limit), u1 = fminf(fmaxf(u.y, -limit), limit);
+                o2[k] = __floats2bfloat162_rn(w * (g0 / (1.f + __expf(-act_alpha * g0)) * (u0 + 1.f)),
+                                              w * (g1 / (1.f + __expf(-act_alpha * g1)) * (u1 + 1.f)));
+            }
+        }
+        *reinterpret_cast<uint4*>(y + (t * experts + e) * (size_t)ff + pc * 8) = out;
+    }
+}
+
 extern "C" int lb_moe_activation(const void* gu, const float* dense, void* y, int tokens, int experts, int ff, int n, float limit,
                                  float act_alpha, int dtype, void* stream) {
     if (tokens <= 0 || experts <= 0) return kOk;
     if (ff <= 0 || n < experts || experts > 65535) return kBadSize;
+    if (dtype == kBF16 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)y) & 15) == 0) {
+        moe_activation_vec_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, dense, (__nv_bfloat16*)y, experts, ff,
+                                                                          n, limit, act_alpha);
+        return launch_status();
+    }
     dim3 grid((ff + 127) / 128, experts, tokens);
     LB_DISPATCH_DTYPE(dtype, moe_activation_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
         (const T*)gu, dense, (T*)y, experts, ff, n, limit, act_alpha));

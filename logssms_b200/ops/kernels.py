@@ -1210,6 +1210,11 @@ def heads_matmul(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     T, H, Kd = a.shape
     _need(a.stride(2) == 1 and w.is_contiguous() and w.shape[:2] == (H, Kd) and w.dtype == a.dtype, "heads_matmul wants a [T, H, K] and w [H, K, N]")
     N = w.shape[2]
+    if out is None and a.dtype == torch.bfloat16 and T > SKINNY_MAX_ROWS:
+        # many rows: the library's batched product over the heads (as `linear` leaves its products of many rows to it);
+        # the result is a [T, H, N] view of its [H, T, N] output
+        product = lambda: torch.bmm(a.transpose(0, 1), w).transpose(0, 1)
+        return PROFILER.timed("library", "bmm", product) if PROFILER.enabled else product()
     if out is None:
         out = torch.empty((T, H, N), dtype=a.dtype, device=a.device)
     _need(out.shape == (T, H, N) and out.stride(2) == 1 and out.dtype == a.dtype, "out must be [T, H, N]")
@@ -1276,8 +1281,8 @@ def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.T
     T, H, rank = qa.shape
     rot = kr_cache.shape[-1]
     _need(latent_attention_mma_ok(qa, rot), "latent_attention_mma takes bfloat16, rank a multiple of 32 up to 512, rot a multiple of 16")
-    _need(qa.is_contiguous() and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
-          "q_rot must be [tokens, H, rot] with unit stride in its last axis")
+    _need(qa.stride(2) == 1 and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
+          "qa [tokens, H, rank] and q_rot [tokens, H, rot] must have unit stride in their last axis")
     _need(c_cache.dim() == 3 and c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.shape[2] == rank
           and c_cache.dtype == qa.dtype == kr_cache.dtype and kr_cache.shape[:2] == c_cache.shape[:2], "latent caches do not fit the queries")
     for t, name in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
@@ -1289,10 +1294,10 @@ def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.T
     if splits > 1:
         part_o = torch.empty((T * H, splits, rank), dtype=torch.float32, device=qa.device)
         part_ml = torch.empty((T * H, splits, 2), dtype=torch.float32, device=qa.device)
-    f = _fn("attention_latent", "lb_latent_attention_mma", [c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
+    f = _fn("attention_latent", "lb_latent_attention_mma", [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p, c_void_p, c_int,
                                                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
-    _check(f(_ptr(qa), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
+    _check(f(_ptr(qa), qa.stride(0), qa.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache), _ptr(block_table),
              block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), T if blocks is None else blocks.shape[0], _ptr(out), _ptr(part_o),
              _ptr(part_ml), T, H, rank, rot, c_cache.shape[1], scale, window, splits, _stream()), "latent_attention_mma",
            f"(rank {rank}, rot {rot})", launches=2 if splits > 1 else 1)

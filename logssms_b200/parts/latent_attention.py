@@ -85,7 +85,8 @@ class LatentAttention(Part):
                                          ctx.positions, blocks, s.softmax_scale, s.window or 0,
                                          splits=K.latent_splits(n_blocks, H, keys))
         else:
+            qa = qa if qa.is_contiguous() else qa.contiguous()
             lat = K.latent_attention(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
                                      ctx.positions, s.softmax_scale, s.window or 0)
         o = K.heads_matmul(lat, self.uv_t)                                 # [T, H, value]
-        return K.linear(o.view(T, H * s.value_dim), self.o_w)
+        return K.linear(o.reshape(T, H * s.value_dim), self.o_w)

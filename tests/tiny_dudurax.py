@@ -57,7 +57,19 @@ DUDU_C = _model(48, 130, 1e-5, 3.0, 1.0, 1, 1, 1, [
     {**_latent(1, 2, 2, 2, 1, 1, 3), "mlp": None},
 ])
 
-DUDU = {"A": DUDU_A, "B": DUDU_B, "C": DUDU_C}
+# D: recurrent layers only (no paged cache at all); E: attention layers only (no state but the previous token), two
+# of them with equal needs (one page group) and one with others
+DUDU_D = _model(40, 90, 1e-5, 1.5, 3.0, 13, 5, 3, [
+    {**_gla("gla", 2, 32, 16, 8.0, 4), "mlp": {"kind": "dense", "ff": 64}},
+    {**_gla("gla_2", 2, 16, 32, 2.0, 4), "mlp": _moe(16, 1.5, 2, 1, 1, 1, 2, 1.0)},
+])
+DUDU_E = _model(48, 77, 1e-5, 2.5, 5.0, 31, 7, 11, [
+    {**_latent(4, 8, 16, 16, 8, 32, 48), "mlp": None},
+    {**_latent(4, 8, 16, 16, 8, 32, 48), "mlp": {"kind": "dense", "ff": 64}},
+    {**_latent(2, 16, 16, 8, 24, 64, 9), "mlp": _moe(24, 3.0, 3, 1, 2, 1, 2, 1.5)},
+])
+
+DUDU = {"A": DUDU_A, "B": DUDU_B, "C": DUDU_C, "D": DUDU_D, "E": DUDU_E}
 
 
 def make_dudurax_dir(path, raw: dict, seed: int = 0, dtype=torch.float32, sharp: float = 1.0, steady_router: bool = False) -> str:
