@@ -245,6 +245,24 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(gmem_src) : "memory");
 }
+// four (two) 8x8 tiles of 16-bit values from shared memory into the fragment layout of `mma.sync`; lane 8i + r gives the
+// address of row r of tile i; `_t`: every tile transposed on the way
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t* r, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
 __device__ __forceinline__ uint32_t pack_bf16(__nv_bfloat16 lo, __nv_bfloat16 hi) {
     return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
 }
@@ -305,11 +323,13 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     // key tiles come by 16-byte asynchronous copies into two buffers: the next tile travels while this one is used
     auto stage = [&](int tile, bf* dstbase) {
         const int j0 = key_lo + tile * kMmaKeys;
+        // every lane looks up the cache row of one key of the tile (one trip to the page table, not one per row)
+        const int jl = j0 + lane;
+        const long long mine = jl <= p_hi ? (long long)pages[jl / page_size] * page_size + jl % page_size : -1;
         for (int jj = warp; jj < kMmaKeys; jj += 4) {
-            const int j = j0 + jj;
+            const long long off = __shfl_sync(0xffffffffu, mine, jj);
             bf* dst = dstbase + jj * DP;
-            if (j <= p_hi) {
-                const size_t off = (size_t)pages[j / page_size] * page_size + j % page_size;
+            if (off >= 0) {
                 const bf* c4 = c_cache + off * rank;
                 const bf* k4 = kr_cache + off * rot;
                 for (int i = lane; i < rank / 8; i += 32) cp_async_16(dst + i * 8, c4 + i * 8);
@@ -329,14 +349,25 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
         if (tile + 1 < tile_hi) stage(tile + 1, Kt0 + ((tile + 1 - tile_lo) & 1) * kMmaKeys * DP);
         // scores of this warp's 8 keys
         float s[4] = {0.f, 0.f, 0.f, 0.f};
-        const bf* kb = Kt + (warp * 8 + g) * DP;
-        for (int kk = 0; kk < D; kk += 16) {
-            uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t);
-            a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t);
-            a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * DP + kk + 2 * t + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * DP + kk + 2 * t + 8);
-            mma_16816(s, a, *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t), *reinterpret_cast<const uint32_t*>(kb + kk + 2 * t + 8));
+        {
+            // A: the 16 query rows (tiles: rows 0-7 | 8-15 at k, then at k + 8); B: this warp's 8 keys (k, k + 8, k + 16, k + 24)
+            const bf* qp = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + (lane >> 4) * 8;
+            const bf* kp = Kt + (warp * 8 + (lane & 7)) * DP + (lane >> 3) * 8;
+            int kk = 0;
+            for (; kk + 32 <= D; kk += 32) {
+                uint32_t a0[4], a1[4], b[4];
+                ldsm_x4(a0, qp + kk);
+                ldsm_x4(a1, qp + kk + 16);
+                ldsm_x4(b, kp + kk);
+                mma_16816(s, a0, b[0], b[1]);
+                mma_16816(s, a1, b[2], b[3]);
+            }
+            if (kk < D) {
+                uint32_t a0[4], b[2];
+                ldsm_x4(a0, qp + kk);
+                ldsm_x2(b, kp + kk);                     // (lanes 16-31 give addresses that are not used)
+                mma_16816(s, a0, b[0], b[1]);
+            }
         }
         const int jk = j0 + warp * 8 + 2 * t;
         s[0] = (jk >= lo0 && jk <= hi0) ? s[0] * scale : -INFINITY;
@@ -373,16 +404,20 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
 #pragma unroll
         for (int ks = 0; ks < kMmaKeys; ks += 16) {
             uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(Ps + g * PP + ks + 2 * t);
-            a[1] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * PP + ks + 2 * t);
-            a[2] = *reinterpret_cast<const uint32_t*>(Ps + g * PP + ks + 2 * t + 8);
-            a[3] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * PP + ks + 2 * t + 8);
-            const bf* v0 = Kt + (ks + 2 * t) * DP + colw + g;
+            ldsm_x4(a, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * PP + ks + (lane >> 4) * 8);
+            // B: 16 keys x 8 columns per output tile, transposed on the way; two output tiles per load
+            const bf* vp = Kt + (ks + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + colw + (lane >> 4) * 8;
 #pragma unroll
-            for (int nt = 0; nt < NTW; ++nt) {
-                if (nt < ntw) {
-                    const bf* vp = v0 + nt * 8;
-                    mma_16816(acc[nt], a, pack_bf16(vp[0], vp[DP]), pack_bf16(vp[8 * DP], vp[9 * DP]));
+            for (int nt = 0; nt < NTW; nt += 2) {
+                if (nt + 1 < ntw) {
+                    uint32_t b[4];
+                    ldsm_x4_t(b, vp + nt * 8);
+                    mma_16816(acc[nt], a, b[0], b[1]);
+                    mma_16816(acc[nt + 1], a, b[2], b[3]);
+                } else if (nt < ntw) {
+                    uint32_t b[2];
+                    ldsm_x2_t(b, vp + nt * 8);
+                    mma_16816(acc[nt], a, b[0], b[1]);
                 }
             }
         }
