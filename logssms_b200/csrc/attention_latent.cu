@@ -457,6 +457,215 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(
     }
 }
 
+// The same for prompt portions: a CTA holds 4 / CH tiles of 16 rows (up to 64 (token, head) rows of neighbouring tokens
+// of one request), so a staged key tile serves four times the rows.  A warp owns one row tile (CH = 2: two warps share
+// a row tile and split the output columns): it computes all 32 scores of its rows, keeps the weights in registers (the
+// accumulator layout of the score tiles is the operand layout of the next product) and its running output in
+// registers; warps meet only at the one barrier per key tile that guards the two staging buffers.
+// grid (token blocks, head groups); NTW: 8-column output tiles per warp (rank / CH <= 8 * NTW)
+template <int NTW, int CH>
+__global__ void __launch_bounds__(128) latent_attention_wide_kernel(
+        const __nv_bfloat16* __restrict__ qa, long qa_row, long qa_head, const __nv_bfloat16* __restrict__ q_rot, long q_rot_row,
+        long q_rot_head, const __nv_bfloat16* __restrict__ c_cache, const __nv_bfloat16* __restrict__ kr_cache,
+        const int* __restrict__ block_table, int table_width, const int* __restrict__ token_req,
+        const int* __restrict__ positions, const int* __restrict__ blocks, __nv_bfloat16* __restrict__ out,
+        int H, int rank, int rot, int page_size, float scale, int window) {
+    typedef __nv_bfloat16 bf;
+    constexpr int RT = 4 / CH, ROWS = RT * 16;
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int D = rank + rot, DP = D + 8;
+    bf* Qs = reinterpret_cast<bf*>(raw);                    // [ROWS][DP]
+    bf* Kt0 = Qs + ROWS * DP;                               // two buffers of [32][DP]
+    __shared__ int row_lo[ROWS], row_hi[ROWS];
+    const int t0 = blocks[2 * blockIdx.x], ntok = blocks[2 * blockIdx.x + 1];
+    if (t0 < 0) return;
+    const int h0 = H >= 16 ? blockIdx.y * 16 : 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int rt = warp / CH, half = warp % CH;
+    const int* pages = block_table + (size_t)token_req[t0] * table_width;
+    // row r of the CTA -> (token of the block, head); -1: no such row
+    auto row_token = [&](int r) { const int tok = H >= 16 ? r / 16 : r / H; return (tok < ntok && (H < 16 || h0 + r % 16 < H)) ? tok : -1; };
+    auto row_head = [&](int r) { return H >= 16 ? h0 + r % 16 : r % H; };
+    if (threadIdx.x < ROWS) {
+        const int tok = row_token(threadIdx.x);
+        int lo = 1, hi = 0;
+        if (tok >= 0) {
+            hi = positions[t0 + tok];
+            lo = window > 0 ? max(0, hi - window + 1) : 0;
+        }
+        row_lo[threadIdx.x] = lo; row_hi[threadIdx.x] = hi;
+    }
+    for (int i = threadIdx.x; i < ROWS * (D / 8); i += blockDim.x) {
+        const int r = i / (D / 8), pc = (i % (D / 8)) * 8, tok = row_token(r);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok >= 0) {
+            const int h = row_head(r);
+            const bf* src = pc < rank ? qa + (size_t)(t0 + tok) * qa_row + (size_t)h * qa_head + pc
+                                      : q_rot + (size_t)(t0 + tok) * q_rot_row + (size_t)h * q_rot_head + pc - rank;
+            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) v = *reinterpret_cast<const uint4*>(src);
+            else { bf* e = reinterpret_cast<bf*>(&v); for (int k = 0; k < 8; ++k) e[k] = src[k]; }
+        }
+        *reinterpret_cast<uint4*>(Qs + r * DP + pc) = v;
+    }
+    const int p_hi = positions[t0 + ntok - 1], p_first = positions[t0];
+    const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int tiles = (p_hi - key_lo + kMmaKeys) / kMmaKeys;
+    float acc[NTW][4];
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int ntw = rank / CH / 8;
+    const int colw = half * (rank / CH);
+    auto stage = [&](int tile, bf* dstbase) {
+        const int j0 = key_lo + tile * kMmaKeys;
+        const int jl = j0 + lane;
+        const long long mine = jl <= p_hi ? (long long)pages[jl / page_size] * page_size + jl % page_size : -1;
+        for (int jj = warp; jj < kMmaKeys; jj += 4) {
+            const long long off = __shfl_sync(0xffffffffu, mine, jj);
+            bf* dst = dstbase + jj * DP;
+            if (off >= 0) {
+                const bf* c4 = c_cache + off * rank;
+                const bf* k4 = kr_cache + off * rot;
+                for (int i = lane; i < rank / 8; i += 32) cp_async_16(dst + i * 8, c4 + i * 8);
+                for (int i = lane; i < rot / 8; i += 32) cp_async_16(dst + rank + i * 8, k4 + i * 8);
+            } else {
+                for (int i = lane; i < D / 8; i += 32) reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, Kt0);
+    __syncthreads();
+    const int lo0 = row_lo[rt * 16 + g], hi0 = row_hi[rt * 16 + g], lo1 = row_lo[rt * 16 + g + 8], hi1 = row_hi[rt * 16 + g + 8];
+    const bf* qp = Qs + (rt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + (lane >> 4) * 8;
+    for (int tile = 0; tile < tiles; ++tile) {
+        const int j0 = key_lo + tile * kMmaKeys;
+        bf* Kt = Kt0 + (tile & 1) * kMmaKeys * DP;
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();                                     // this tile has landed; the tile before is used up
+        if (tile + 1 < tiles) stage(tile + 1, Kt0 + ((tile + 1) & 1) * kMmaKeys * DP);
+        float s[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+        const bf* kp = Kt + (lane & 7) * DP + (lane >> 3) * 8;
+        int kk = 0;
+        for (; kk + 32 <= D; kk += 32) {
+            uint32_t a0[4], a1[4];
+            ldsm_x4(a0, qp + kk);
+            ldsm_x4(a1, qp + kk + 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b[4];
+                ldsm_x4(b, kp + j * 8 * DP + kk);
+                mma_16816(s[j], a0, b[0], b[1]);
+                mma_16816(s[j], a1, b[2], b[3]);
+            }
+        }
+        if (kk < D) {
+            uint32_t a0[4];
+            ldsm_x4(a0, qp + kk);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t b[2];
+                ldsm_x2(b, kp + j * 8 * DP + kk);
+                mma_16816(s[j], a0, b[0], b[1]);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int jk = j0 + j * 8 + 2 * t;
+            s[j][0] = (jk >= lo0 && jk <= hi0) ? s[j][0] * scale : -INFINITY;
+            s[j][1] = (jk + 1 >= lo0 && jk + 1 <= hi0) ? s[j][1] * scale : -INFINITY;
+            s[j][2] = (jk >= lo1 && jk <= hi1) ? s[j][2] * scale : -INFINITY;
+            s[j][3] = (jk + 1 >= lo1 && jk + 1 <= hi1) ? s[j][3] * scale : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+        const float c0 = mn0 == -INFINITY ? 1.f : expf(m[0] - mn0), c1 = mn1 == -INFINITY ? 1.f : expf(m[1] - mn1);
+        m[0] = mn0; m[1] = mn1;
+        uint32_t pa[4][2];                                   // the weights, rounded, as operand pieces: [key tile][row half]
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 w0 = __floats2bfloat162_rn(mn0 == -INFINITY ? 0.f : expf(s[j][0] - mn0), mn0 == -INFINITY ? 0.f : expf(s[j][1] - mn0));
+            const __nv_bfloat162 w1 = __floats2bfloat162_rn(mn1 == -INFINITY ? 0.f : expf(s[j][2] - mn1), mn1 == -INFINITY ? 0.f : expf(s[j][3] - mn1));
+            sum0 += __bfloat162float(w0.x) + __bfloat162float(w0.y);      // the sums take the weights as the product sees them
+            sum1 += __bfloat162float(w1.x) + __bfloat162float(w1.y);
+            pa[j][0] = *reinterpret_cast<const uint32_t*>(&w0);
+            pa[j][1] = *reinterpret_cast<const uint32_t*>(&w1);
+        }
+        l[0] = l[0] * c0 + sum0;
+        l[1] = l[1] * c1 + sum1;
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            if (nt < ntw) { acc[nt][0] *= c0; acc[nt][1] *= c0; acc[nt][2] *= c1; acc[nt][3] *= c1; }
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            const uint32_t a[4] = {pa[2 * ks][0], pa[2 * ks][1], pa[2 * ks + 1][0], pa[2 * ks + 1][1]};
+            const bf* vp = Kt + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * DP + colw + (lane >> 4) * 8;
+#pragma unroll
+            for (int nt = 0; nt < NTW; nt += 2) {
+                if (nt + 1 < ntw) {
+                    uint32_t b[4];
+                    ldsm_x4_t(b, vp + nt * 8);
+                    mma_16816(acc[nt], a, b[0], b[1]);
+                    mma_16816(acc[nt + 1], a, b[2], b[3]);
+                } else if (nt < ntw) {
+                    uint32_t b[2];
+                    ldsm_x2_t(b, vp + nt * 8);
+                    mma_16816(acc[nt], a, b[0], b[1]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 1);
+        l[e] += __shfl_xor_sync(0xffffffffu, l[e], 2);
+        const int r = rt * 16 + g + 8 * e, tok = row_token(r);
+        if (tok < 0) continue;
+        const size_t row = (size_t)(t0 + tok) * H + row_head(r);
+        const float inv = l[e] > 0.f ? 1.f / l[e] : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt)
+            if (nt < ntw)
+                *reinterpret_cast<__nv_bfloat162*>(out + row * rank + colw + nt * 8 + 2 * t) =
+                    __floats2bfloat162_rn(acc[nt][2 * e] * inv, acc[nt][2 * e + 1] * inv);
+    }
+}
+
+// blocks: runs of at most `wide_tokens(H, rank)` neighbouring tokens of one request, every token of the step in one.
+extern "C" int lb_latent_wide_tokens(int H, int rank) {
+    const int rows = rank > 256 ? 32 : 64;
+    return H >= 16 ? rows / 16 : rows / H;
+}
+
+extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_head, const void* q_rot, long q_rot_row, long q_rot_head,
+                                        const void* c_cache, const void* kr_cache, const int* block_table, int table_width,
+                                        const int* token_req, const int* positions, const int* blocks, int num_blocks, void* out,
+                                        int H, int rank, int rot, int page_size, float scale, int window, void* stream) {
+    if (num_blocks <= 0) return kOk;
+    if (H <= 0 || rank <= 0 || rank % 32 || rot < 0 || rot % 16 || page_size <= 0 || window < 0) return kBadSize;
+    if (rank > 512) return kTooLarge;
+    typedef __nv_bfloat16 bf;
+    const int D = rank + rot, rows = rank > 256 ? 32 : 64;
+    const size_t smem = (size_t)(rows + 2 * kMmaKeys) * (D + 8) * sizeof(bf);
+    dim3 grid(num_blocks, H >= 16 ? (H + 15) / 16 : 1);
+    cudaStream_t st = (cudaStream_t)stream;
+#define LB_LW(NTW_, CH_) { static size_t have = 0; ensure_dynamic_smem(latent_attention_wide_kernel<NTW_, CH_>, smem, have); \
+        latent_attention_wide_kernel<NTW_, CH_><<<grid, 128, smem, st>>>((const bf*)qa, qa_row, qa_head, (const bf*)q_rot, q_rot_row, \
+            q_rot_head, (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, \
+            H, rank, rot, page_size, scale, window); }
+    if (rank <= 128) LB_LW(16, 1) else if (rank <= 256) LB_LW(32, 1) else LB_LW(32, 2)
+#undef LB_LW
+    return launch_status();
+}
+
 // grid (listed token blocks' rows): one CTA per (token, head) row of the step
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int rank, int splits) {

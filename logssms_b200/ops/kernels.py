@@ -1304,6 +1304,39 @@ def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.T
     return out
 
 
+def latent_wide_tokens(num_heads: int, rank: int) -> int:
+    """Most neighbouring tokens of one request in a block of `latent_attention_wide` (its work list:
+    `StepContext.token_blocks` of this many)."""
+    rows = 32 if rank > 256 else 64
+    return rows // 16 if num_heads >= 16 else rows // num_heads
+
+
+def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
+                          block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, blocks: torch.Tensor,
+                          scale: float, window: int = 0) -> torch.Tensor:
+    """`latent_attention_mma` for steps with prompt portions: a CTA holds up to 64 (token, head) rows of neighbouring
+    tokens, so a staged key tile serves four times the rows, and a warp keeps its rows' weights in registers.
+    `blocks`: `StepContext.token_blocks(latent_wide_tokens(H, rank))`."""
+    _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks)
+    T, H, rank = qa.shape
+    rot = kr_cache.shape[-1]
+    _need(latent_attention_mma_ok(qa, rot), "latent_attention_wide takes bfloat16, rank a multiple of 32 up to 512, rot a multiple of 16")
+    _need(qa.stride(2) == 1 and q_rot.shape == (T, H, rot) and (rot == 0 or q_rot.stride(2) == 1) and q_rot.dtype == qa.dtype,
+          "qa [tokens, H, rank] and q_rot [tokens, H, rot] must have unit stride in their last axis")
+    _need(c_cache.dim() == 3 and c_cache.is_contiguous() and kr_cache.is_contiguous() and c_cache.shape[2] == rank
+          and c_cache.dtype == qa.dtype == kr_cache.dtype and kr_cache.shape[:2] == c_cache.shape[:2], "latent caches do not fit the queries")
+    for t, name in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions"), (blocks, "blocks")):
+        _i32(t, name)
+    out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
+    f = _fn("attention_latent", "lb_latent_attention_wide", [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p,
+                                                             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                             c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(qa), qa.stride(0), qa.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache),
+             _ptr(block_table), block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), blocks.shape[0], _ptr(out),
+             H, rank, rot, c_cache.shape[1], scale, window, _stream()), "latent_attention_wide", f"(rank {rank}, rot {rot})")
+    return out
+
+
 # --------------------------------------------------------------------------- routed feed-forward
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, num_experts: int, top: int, groups: int,
               keep: int, scale: float):

@@ -186,6 +186,21 @@ def test_latent_attention_in_portions_with_windows_around_page_edges(dtype, head
             close(y, P.latent_attention(x.double(), w, {}, **kw), dtype)
 
 
+@pytest.mark.parametrize("heads, nope, rot, rank, window", [(16, 16, 16, 64, 70), (5, 8, 16, 32, 33), (20, 8, 32, 288, 40), (2, 16, 16, 96, 1000)])
+def test_latent_attention_of_long_portions_shares_key_tiles_between_neighbouring_tokens(heads, nope, rot, rank, window):
+    """Portions of hundreds of tokens (bfloat16): the form whose CTAs hold up to 64 (token, head) rows, for 16 and more
+    heads (a tile is one token), fewer heads (several tokens per tile, uneven when 64 is no multiple), ranks beyond 256
+    (two warps share a row tile), beside a short request, with a window shorter and longer than the portions."""
+    dtype = torch.bfloat16
+    part, w, kw = latent_part(dtype, heads, nope, rot, rot, 8, rank, window, seed=heads, sharp=2.0, page_size=16, max_seq_len=1024)
+    cache, planner = cache_for([part.cache_needs()], dtype, num_pages=120, max_requests=3, max_seq_len=1024)
+    lengths = [700, 9, 420]
+    xs = inputs(lengths, 56, dtype, seed=2)
+    got = step_in_portions(planner, cache, lengths, [[300, 2, 0], [250, 1, 420], [150, 6, 0]], lambda ctx, spans: part.forward(rows_of(xs, spans), ctx, 0))
+    for x, y in zip(xs, got):
+        close(y, P.latent_attention(x.double(), w, {}, **kw), dtype)
+
+
 @pytest.mark.parametrize("window", [1, 2, 15, 16, 17, 31, 32, 33, 100])
 def test_latent_attention_kernel_sees_exactly_the_window(window):
     """Equal scores everywhere and latents that carry their own position: the output's first column is then the mean
