@@ -228,6 +228,40 @@ def test_latent_attention_kernel_sees_exactly_the_window(window):
     assert float(out2[5, 0, 0]) == -7.0
 
 
+@pytest.mark.parametrize("heads", [4, 16])
+@pytest.mark.parametrize("window", [1, 2, 16, 17, 31, 32, 33, 64, 65, 100])
+def test_tensor_core_latent_attention_sees_exactly_the_window(window, heads):
+    """The tensor-core forms (bfloat16), equal scores everywhere, and a mark in the latents of every `window`-th key: any
+    `window` keys in a row hold exactly one mark, so the output's first column is 1 / (keys seen) at every position; a
+    window one key too wide would see two marks at some positions, one key too narrow none."""
+    import numpy as np
+    from logssms_b200.ops import kernels as K
+    from logssms_b200.parts.context import token_block_list
+    page, n, rank, rot = 16, 150, 32, 16
+    order = [3, 0, 9, 5, 1, 4, 8, 2, 7, 6]
+    c = torch.zeros(11, page, rank)
+    for j in range(0, n, window):
+        c[order[j // page], j % page, 0] = 1.0
+    c, kr = c.to(torch.bfloat16).cuda(), torch.zeros(11, page, rot, dtype=torch.bfloat16).cuda()
+    table = torch.tensor([order], dtype=torch.int32).cuda()
+    pos = torch.arange(n, dtype=torch.int32).cuda()
+    req = torch.zeros(n, dtype=torch.int32).cuda()
+    qa = torch.zeros(n, heads, rank, dtype=torch.bfloat16).cuda()
+    qr = torch.zeros(n, heads, rot, dtype=torch.bfloat16).cuda()
+    want = 1.0 / torch.minimum(torch.arange(n) + 1, torch.tensor(window)).double()
+    per = K.latent_wide_tokens(heads, rank)
+    blocks = torch.from_numpy(np.ascontiguousarray(token_block_list([n], per))).cuda()
+    outs = {"a tile per token": K.latent_attention_mma(qa, qr, c, kr, table, req, pos, None, 1.0, window),
+            "key ranges": K.latent_attention_mma(qa, qr, c, kr, table, req, pos, None, 1.0, window, splits=3),
+            "wide": K.latent_attention_wide(qa, qr, c, kr, table, req, pos, blocks, 1.0, window)}
+    small = torch.from_numpy(np.ascontiguousarray(token_block_list([n], max(1, 16 // heads)))).cuda()
+    outs["tokens that share a tile"] = K.latent_attention_mma(qa, qr, c, kr, table, req, pos, small, 1.0, window)
+    for name, out in outs.items():
+        for h in (0, heads - 1):
+            got = out[:, h, 0].double().cpu()
+            assert torch.allclose(got, want, rtol=2e-2, atol=1e-4), f"{name}, head {h}: first position off {int(((got - want).abs() > 2e-2 * want).nonzero()[0])}"
+
+
 # --------------------------------------------------------------------------- feed-forwards
 @pytest.mark.parametrize("n, experts, top, groups, keep", [(6, 4, 2, 3, 2), (12, 8, 4, 4, 3), (3, 3, 1, 1, 1), (6, 2, 3, 2, 1),
                                                            (64, 60, 8, 8, 4), (2, 1, 2, 2, 2), (5, 0, 2, 1, 1)])
