@@ -15,7 +15,7 @@
 using namespace lb200;
 
 constexpr int kRouteMax = 256;        // router outputs
-constexpr int kRouteWarps = 8;        // warps of a token's CTA: each takes every eighth router output
+constexpr int kRouteWarps = 16;       // warps of a token's CTA: each takes every sixteenth router output
 
 // grid (tokens)
 template <typename T>

@@ -74,7 +74,7 @@ def replayed(tmp_path_factory, name, dtype):
 
 @pytest.mark.parametrize("scenario", SCENARIOS)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "R1", "R2", "R3"])
 def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
     got, want, ids_of, trace = replayed(tmp_path_factory, name, dtype)
     checked = 0

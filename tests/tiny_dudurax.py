@@ -69,7 +69,39 @@ DUDU_E = _model(48, 77, 1e-5, 2.5, 5.0, 31, 7, 11, [
     {**_latent(2, 16, 16, 8, 24, 64, 9), "mlp": _moe(24, 3.0, 3, 1, 2, 1, 2, 1.5)},
 ])
 
+def random_dudurax(seed: int) -> dict:
+    """A configuration with every size and option drawn at random within what config.json allows."""
+    import random
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(2, 5)):
+        if rng.random() < 0.55:
+            mixer = _gla(rng.choice(["gla", "gla_2"]), rng.randint(1, 4), rng.choice([8, 16, 24, 32, 48, 64, 80]),
+                         rng.choice([8, 16, 24, 40, 64, 72]), rng.choice([1.0, 2.0, 4.0, 16.0, 64.0]), rng.randint(1, 8))
+        else:
+            rot = rng.choice([8, 16, 32])
+            mixer = _latent(rng.choice([1, 2, 3, 4, 6, 16]), rng.choice([8, 16, 32]), rot, rng.choice([rot, rot // 2]),
+                            rng.choice([8, 16, 24, 40]), rng.choice([16, 24, 32, 40, 64, 96]),
+                            rng.choice([1, 3, 17, 64, 65, 100, 1000]), base=rng.choice([100.0, 1e4, 1e6]))
+        kind = rng.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            mlp = None
+        elif kind == "dense":
+            mlp = {"kind": "dense", "ff": 2 * rng.randint(8, 60)}
+        else:
+            experts, identity = rng.randint(1, 6), rng.randint(0, 3)
+            n = experts + identity
+            count = rng.choice([d for d in range(1, n + 1) if n % d == 0])
+            keep = rng.randint(1, count)
+            mlp = _moe(2 * rng.randint(4, 30), rng.choice([0.5, 1.0, 2.0, 7.0]), experts, identity, count, keep,
+                       rng.randint(1, keep * (n // count)), rng.choice([1.0, 1.5, 2.5]))
+        layers.append({**mixer, "mlp": mlp})
+    return _model(2 * rng.randint(16, 48), rng.randint(60, 400), rng.choice([1e-5, 1e-6]), rng.choice([1.0, 2.0, 3.0]),
+                  rng.choice([1.0, 4.0, 12.0]), rng.randint(1, 2000), rng.randint(1, 200), rng.randint(1, 200), layers)
+
+
 DUDU = {"A": DUDU_A, "B": DUDU_B, "C": DUDU_C, "D": DUDU_D, "E": DUDU_E}
+DUDU.update({f"R{seed}": random_dudurax(seed) for seed in range(1, 25)})
 
 
 def make_dudurax_dir(path, raw: dict, seed: int = 0, dtype=torch.float32, sharp: float = 1.0, steady_router: bool = False) -> str:
