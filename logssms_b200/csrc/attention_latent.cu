@@ -640,20 +640,22 @@ __global__ void __launch_bounds__(128) latent_attention_wide_kernel(
 }
 
 // blocks: runs of at most `wide_tokens(H, rank)` neighbouring tokens of one request, every token of the step in one.
-extern "C" int lb_latent_wide_tokens(int H, int rank) {
-    const int rows = rank > 256 ? 32 : 64;
+// `rows`: 64 (a warp per row tile; rank <= 256) or 32 (two warps per row tile, half the output columns each: more,
+// lighter CTAs, every score computed twice)
+extern "C" int lb_latent_wide_tokens(int H, int rows) {
     return H >= 16 ? rows / 16 : rows / H;
 }
 
 extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_head, const void* q_rot, long q_rot_row, long q_rot_head,
                                         const void* c_cache, const void* kr_cache, const int* block_table, int table_width,
                                         const int* token_req, const int* positions, const int* blocks, int num_blocks, void* out,
-                                        int H, int rank, int rot, int page_size, float scale, int window, void* stream) {
+                                        int H, int rank, int rot, int page_size, float scale, int window, int rows, void* stream) {
     if (num_blocks <= 0) return kOk;
     if (H <= 0 || rank <= 0 || rank % 32 || rot < 0 || rot % 16 || page_size <= 0 || window < 0) return kBadSize;
+    if ((rows != 32 && rows != 64) || (rows == 64 && rank > 256)) return kBadSize;
     if (rank > 512) return kTooLarge;
     typedef __nv_bfloat16 bf;
-    const int D = rank + rot, rows = rank > 256 ? 32 : 64;
+    const int D = rank + rot;
     const size_t smem = (size_t)(rows + 2 * kMmaKeys) * (D + 8) * sizeof(bf);
     dim3 grid(num_blocks, H >= 16 ? (H + 15) / 16 : 1);
     cudaStream_t st = (cudaStream_t)stream;
@@ -661,7 +663,8 @@ extern "C" int lb_latent_attention_wide(const void* qa, long qa_row, long qa_hea
         latent_attention_wide_kernel<NTW_, CH_><<<grid, 128, smem, st>>>((const bf*)qa, qa_row, qa_head, (const bf*)q_rot, q_rot_row, \
             q_rot_head, (const bf*)c_cache, (const bf*)kr_cache, block_table, table_width, token_req, positions, blocks, (bf*)out, \
             H, rank, rot, page_size, scale, window); }
-    if (rank <= 128) LB_LW(16, 1) else if (rank <= 256) LB_LW(32, 1) else LB_LW(32, 2)
+    if (rows == 64) { if (rank <= 128) LB_LW(16, 1) else LB_LW(32, 1) }
+    else { if (rank <= 256) LB_LW(16, 2) else LB_LW(32, 2) }
 #undef LB_LW
     return launch_status();
 }

@@ -1304,19 +1304,26 @@ def latent_attention_mma(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.T
     return out
 
 
-def latent_wide_tokens(num_heads: int, rank: int) -> int:
-    """Most neighbouring tokens of one request in a block of `latent_attention_wide` (its work list:
-    `StepContext.token_blocks` of this many)."""
-    rows = 32 if rank > 256 else 64
+def latent_wide_rows(num_tokens: int, num_heads: int, rank: int) -> int:
+    """Rows of a CTA of `latent_attention_wide`: 64 (a warp per tile of 16 rows) where the rank fits a warp's registers,
+    else 32 (two warps per row tile, each with half of the output columns).  (32 rows for more, lighter CTAs on a short
+    prompt was measured too: a 2,048-token prompt of 8 heads at rank 256, 256 CTAs of 64 rows against 512 of 32: 0.288
+    against 0.298 ms for the mixer.)"""
+    return 64 if rank <= 256 else 32
+
+
+def latent_wide_tokens(num_heads: int, rows: int) -> int:
+    """Most neighbouring tokens of one request in a block of `latent_attention_wide` with `rows` rows per CTA (its work
+    list: `StepContext.token_blocks` of this many)."""
     return rows // 16 if num_heads >= 16 else rows // num_heads
 
 
 def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor,
                           block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor, blocks: torch.Tensor,
-                          scale: float, window: int = 0) -> torch.Tensor:
-    """`latent_attention_mma` for steps with prompt portions: a CTA holds up to 64 (token, head) rows of neighbouring
-    tokens, so a staged key tile serves four times the rows, and a warp keeps its rows' weights in registers.
-    `blocks`: `StepContext.token_blocks(latent_wide_tokens(H, rank))`."""
+                          scale: float, window: int = 0, rows: int = 32) -> torch.Tensor:
+    """`latent_attention_mma` for steps with prompt portions: a CTA holds `rows` (32 or 64) (token, head) rows of
+    neighbouring tokens, so a staged key tile serves more rows, and a warp keeps its rows' weights in registers.
+    `blocks`: `StepContext.token_blocks(latent_wide_tokens(H, rows))`."""
     _cuda(qa, q_rot, c_cache, kr_cache, block_table, token_req, positions, blocks)
     T, H, rank = qa.shape
     rot = kr_cache.shape[-1]
@@ -1330,10 +1337,10 @@ def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.
     out = torch.empty((T, H, rank), dtype=qa.dtype, device=qa.device)
     f = _fn("attention_latent", "lb_latent_attention_wide", [c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_void_p,
                                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                                             c_int, c_int, c_int, c_float, c_int, c_void_p])
+                                                             c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(qa), qa.stride(0), qa.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(c_cache), _ptr(kr_cache),
              _ptr(block_table), block_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(blocks), blocks.shape[0], _ptr(out),
-             H, rank, rot, c_cache.shape[1], scale, window, _stream()), "latent_attention_wide", f"(rank {rank}, rot {rot})")
+             H, rank, rot, c_cache.shape[1], scale, window, rows, _stream()), "latent_attention_wide", f"(rank {rank}, rot {rot}, rows {rows})")
     return out
 
 

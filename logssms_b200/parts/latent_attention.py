@@ -77,9 +77,10 @@ class LatentAttention(Part):
         qa = K.heads_matmul(q[:, :, :s.nope_dim], self.uk)                 # [T, H, rank]
         if ctx.has_long_portions and T * H >= 2048 and K.latent_attention_mma_ok(qa, s.rot_dim):
             # prompt portions on the tensor cores: up to 64 (token, head) rows of neighbouring tokens share a key tile
-            blocks, _ = ctx.token_blocks(K.latent_wide_tokens(H, s.kv_rank))
+            rows = K.latent_wide_rows(T, H, s.kv_rank)
+            blocks, _ = ctx.token_blocks(K.latent_wide_tokens(H, rows))
             lat = K.latent_attention_wide(qa, q[:, :, s.nope_dim:], c_cache, kr_cache, ctx.block_tables[gi], ctx.token_req,
-                                          ctx.positions, blocks, s.softmax_scale, s.window or 0)
+                                          ctx.positions, blocks, s.softmax_scale, s.window or 0, rows=rows)
         elif ctx.host_lens is not None and K.latent_attention_mma_ok(qa, s.rot_dim):
             # the tensor-core form for few rows: tiles of 16 (token, head) rows that share their keys
             # (a step of single tokens needs no work list: every token is a block of its own)

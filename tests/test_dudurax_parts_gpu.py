@@ -249,11 +249,11 @@ def test_tensor_core_latent_attention_sees_exactly_the_window(window, heads):
     qa = torch.zeros(n, heads, rank, dtype=torch.bfloat16).cuda()
     qr = torch.zeros(n, heads, rot, dtype=torch.bfloat16).cuda()
     want = 1.0 / torch.minimum(torch.arange(n) + 1, torch.tensor(window)).double()
-    per = K.latent_wide_tokens(heads, rank)
-    blocks = torch.from_numpy(np.ascontiguousarray(token_block_list([n], per))).cuda()
     outs = {"a tile per token": K.latent_attention_mma(qa, qr, c, kr, table, req, pos, None, 1.0, window),
-            "key ranges": K.latent_attention_mma(qa, qr, c, kr, table, req, pos, None, 1.0, window, splits=3),
-            "wide": K.latent_attention_wide(qa, qr, c, kr, table, req, pos, blocks, 1.0, window)}
+            "key ranges": K.latent_attention_mma(qa, qr, c, kr, table, req, pos, None, 1.0, window, splits=3)}
+    for rows in (32, 64):
+        blocks = torch.from_numpy(np.ascontiguousarray(token_block_list([n], K.latent_wide_tokens(heads, rows)))).cuda()
+        outs[f"wide, {rows} rows"] = K.latent_attention_wide(qa, qr, c, kr, table, req, pos, blocks, 1.0, window, rows=rows)
     small = torch.from_numpy(np.ascontiguousarray(token_block_list([n], max(1, 16 // heads)))).cuda()
     outs["tokens that share a tile"] = K.latent_attention_mma(qa, qr, c, kr, table, req, pos, small, 1.0, window)
     for name, out in outs.items():
