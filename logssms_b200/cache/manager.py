@@ -39,9 +39,16 @@ class PagedTensor:
 
 @dataclass(frozen=True)
 class PagedNeed:
-    """What a cache layer keeps per token, in pages: named tensors; `window`: only the last so many tokens are read."""
+    """What a cache layer keeps per token, in pages: named tensors; `window`: only the last so many tokens are read.
+    `every` > 1: one entry per run of so many tokens instead of one per token (a summary of every block of tokens);
+    entry number position // every lies where a token of that number would lie in a group of single tokens."""
     tensors: tuple[PagedTensor, ...]
     window: int | None = None
+    every: int = 1
+
+    def __post_init__(self):
+        if self.every < 1 or (self.every > 1 and self.window is not None):
+            raise ValueError("a paged need has one entry per `every` >= 1 tokens, and a window only with every = 1")
 
 
 def KVNeed(num_kv_heads: int, head_dim: int, window: int | None = None, value_head_dim: int | None = None) -> PagedNeed:
@@ -61,6 +68,11 @@ class StateNeed:
 class CacheNeeds:
     kv: PagedNeed | None = None           # the layer's paged tensors (keys and values, mostly)
     states: tuple[StateNeed, ...] = ()
+    more_paged: tuple[PagedNeed, ...] = ()    # further paged needs of the layer, each with tensor names of its own
+                                              # (block summaries beside the tokens' keys and values, for instance)
+
+    def paged(self) -> tuple[PagedNeed, ...]:
+        return (() if self.kv is None else (self.kv,)) + tuple(self.more_paged)
 
 
 class PageGroup:
@@ -94,7 +106,8 @@ class PageGroup:
         return self.tensor("v", layer)
 
     def pages_for(self, length: int) -> int:
-        return -(-length // self.page_size)
+        """Pages that hold the entries of `length` tokens (a last, unfinished run of `every` tokens has its entry)."""
+        return -(-(-(-length // self.need.every)) // self.page_size)
 
     def lifetime_pages(self, total_len: int, max_step_tokens: int) -> int:
         """Most pages a request of `total_len` tokens holds at any time."""
@@ -132,11 +145,19 @@ class CacheManager:
 
         by_need: dict[PagedNeed, list[int]] = {}
         for layer, need in enumerate(needs):
-            if need.kv is not None:
-                by_need.setdefault(need.kv, []).append(layer)
-        self.groups = [PageGroup(need, layers, num_pages, page_size, max_requests, self.max_pages_per_request,
-                                 dtype, self.device) for need, layers in by_need.items()]
-        self.group_of_layer = {layer: gi for gi, g in enumerate(self.groups) for layer in g.layers}
+            names = [t.name for p in need.paged() for t in p.tensors]
+            if len(set(names)) != len(names):
+                raise ValueError(f"cache layer {layer}: paged tensor names clash: {names}")
+            for p in need.paged():
+                by_need.setdefault(p, []).append(layer)
+        # a group of one entry per `every` tokens needs that much fewer pages (and one for every request's last run)
+        self.groups = [PageGroup(need, layers, num_pages if need.every == 1 else min(num_pages, -(-num_pages // need.every) + max_requests),
+                                 page_size, max_requests, self.max_pages_per_request, dtype, self.device)
+                       for need, layers in by_need.items()]
+        # the group of a layer's keys and values (its first paged need), and of every named paged tensor of a layer
+        self.group_of_layer = {layer: self._group_index(need.kv) for layer, need in enumerate(needs) if need.kv is not None}
+        self.group_of_tensor = {(layer, t.name): gi for gi, g in enumerate(self.groups) for layer in g.layers for t in g.need.tensors
+                                if any(p == g.need and t in p.tensors for p in needs[layer].paged())}
         self._unclaimed = [0] * len(self.groups)     # reserved but not yet handed out, per group
 
         self.states: list[dict[str, torch.Tensor]] = []
@@ -146,11 +167,21 @@ class CacheManager:
                 per_layer[s.name] = torch.zeros((max_requests + 1, *s.shape), dtype=s.dtype or dtype, device=self.device)
             self.states.append(per_layer)
 
+    def _group_index(self, need: PagedNeed) -> int:
+        return next(gi for gi, g in enumerate(self.groups) if g.need == need)
+
+    def paged_tensor(self, layer: int, name: str) -> tuple[torch.Tensor, int]:
+        """([pages, page_size, *shape per entry] of a cache layer's named paged tensor, the index of its page group)."""
+        gi = self.group_of_tensor[(layer, name)]
+        return self.groups[gi].tensor(name, layer), gi
+
     # ------------------------------------------------------------------ sizes
     @staticmethod
     def bytes_per_page(needs: list[CacheNeeds], page_size: int, dtype) -> int:
+        """Bytes that one page of tokens costs over all cache layers (a need of one entry per `every` tokens counts
+        for that fraction)."""
         size = lambda t: int(np.prod(t.shape)) * torch.empty((), dtype=t.dtype or dtype).element_size()
-        return sum(page_size * size(t) for n in needs if n.kv is not None for t in n.kv.tensors)
+        return sum(-(-page_size * size(t) // p.every) for n in needs for p in n.paged() for t in p.tensors)
 
     @staticmethod
     def bytes_per_request_state(needs: list[CacheNeeds], dtype) -> int:

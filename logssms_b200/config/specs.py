@@ -133,7 +133,11 @@ class DenseMLPSpec:
 
 @dataclass(frozen=True)
 class RoutedMLPSpec:
-    """Mixture of clamped gated experts with a softmax router, a choice correction, expert groups and identity experts."""
+    """Mixture of gated experts behind a router, with a choice correction, expert groups and identity experts.
+
+    `score`: "softmax" over all router outputs, or "sigmoid" of each.  `expert`: "clamped" (g~ sigmoid(act_alpha g~)
+    (u~ + 1) with gate and up clamped at `limit`) or "silu" (silu(g) u).  `weigh`: the chosen expert's weight multiplies
+    its "output" or its "input".  `correction`: whether the checkpoint holds a correction of the choice."""
     hidden_size: int
     expert_size: int
     num_experts: int
@@ -144,7 +148,63 @@ class RoutedMLPSpec:
     route_scale: float
     limit: float
     act_alpha: float = 1.702
+    score: str = "softmax"
+    expert: str = "clamped"
+    weigh: str = "output"
+    correction: bool = True
     kind: str = "routed_mlp"
+
+
+@dataclass(frozen=True)
+class ClampedGLUSpec:
+    """Dense gated feed-forward with clamped branches: down(g~ sigmoid(act_alpha g~) (u~ + 1)), g~ = min(gate, limit),
+    u~ = clamp(up, -limit, limit)."""
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    act_alpha: float = 1.702
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class MinGRUSpec:
+    """A gated recurrence per channel whose gates read the current token only: S <- (1 - z) S + z c with z = sigmoid(.),
+    c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0); output product over S * silu(gate)."""
+    hidden_size: int
+    width: int
+    kind: str = "mingru"
+
+
+@dataclass(frozen=True)
+class PooledWindowAttentionSpec:
+    """Grouped-query attention over a sliding window of tokens plus one pooled key/value (the mean) for every block of
+    `pool` tokens that lies wholly behind the window; keys and values of different head sizes; queries and keys rotated
+    over neighbouring pairs of their first `position.rotary_dim` dims, values rotated over all of theirs
+    (`value_position`) and the summed values turned back by the query's position."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    softmax_scale: float
+    window: int
+    pool: int
+    position: RopeSpec | None            # rotation of queries and keys
+    value_position: RopeSpec | None      # rotation of the values (None: values are cached as they are)
+    kind: str = "pooled_window_attention"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself: x <- x + RMSNorm(proj(gelu_tanh(gate x) * e)) with e the columns
+    [offset, offset + dim) of the token's row of a second embedding table that all layers share."""
+    hidden_size: int
+    dim: int
+    offset: int
+    table_width: int
+    vocab_size: int
+    eps: float
+    table_name: str = "side.embed"       # checkpoint name of the shared table, relative to the model
 
 
 @dataclass(frozen=True)
@@ -187,6 +247,25 @@ class PostNormBlockSpec:
     feed_forward_norm_name: str
     skip_scale: float = 1.0
     kind: str = "postnorm"
+
+
+@dataclass(frozen=True)
+class StreamBlockSpec:
+    """Pre-norm block on a 32-bit stream: x <- x + s1 * mixer(norm(x)); with a feed-forward x <- x + s2 * ff(norm(x))
+    (s1, s2: a stored scale per channel, when `layer_scale`); then, with `side`, the token's side input."""
+    prefix: str
+    mixer: MixerSlot
+    mixer_norm: NormSpec
+    mixer_norm_name: str
+    feed_forward: Any                 # None: no feed-forward sublayer (and no second norm or scale)
+    feed_forward_name: str
+    feed_forward_norm: NormSpec | None
+    feed_forward_norm_name: str
+    layer_scale: bool = False
+    layer_scale_names: tuple[str, str] = ("ls1", "ls2")
+    side: TokenSideSpec | None = None
+    side_name: str = "side."
+    kind: str = "prenorm_stream"
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,8 @@
 // Routed feed-forward: the router, the experts' activation, identity experts, and the tanh GELU of dense layers.
 //
 //  moe_route        : 32-bit router per token: logits = W_r h, s = softmax over all n outputs (real and identity
-//                     experts alike); the choice looks at s + correction, restricted to the `keep` groups (of
+//                     experts alike), or with `sigmoid_scores` s = sigmoid of each logit; the choice looks at
+//                     s + correction (if there is one), restricted to the `keep` groups (of
 //                     n / groups neighbours) whose best member scores highest; the `top` best are chosen; their
 //                     weights are s * scale (no correction, no renormalisation).  Writes the dense weights [T, n]
 //                     (0 where not chosen), the chosen indices and weights [T, top], and per token the summed
@@ -9,6 +10,9 @@
 //  moe_activation   : y[t, e, i] = w[t, e] * g~ * sigmoid(act_alpha * g~) * (u~ + 1),  g~ = min(g, limit),
 //                     u~ = clamp(u, -limit, limit), from the packed [gate | up] products of all experts.  The expert's
 //                     weight is applied here, so ONE product with the stacked down matrices sums the experts.
+//                     Mode `kSiluInput`: y = silu(w g) * (w u), the expert silu(gate) * up on an input that was
+//                     multiplied by the weight (gate and up are linear in it).  Without weights (`dense` null, one
+//                     expert) it is the activation of a dense gated layer.
 //  moe_add_identity : out += id_weight[t] * h
 //  gelu_tanh        : 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 #include "lb200/common.cuh"
@@ -23,7 +27,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
         const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ correction,
         float* __restrict__ dense, int* __restrict__ chosen, float* __restrict__ chosen_w,
         float* __restrict__ id_weight, int tokens, int width, int n, int experts, int top,
-        int groups, int keep, float scale) {
+        int groups, int keep, float scale, int sigmoid_scores) {
     __shared__ float z[kRouteMax];
     __shared__ float c[kRouteMax];
     __shared__ unsigned char ok[kRouteMax];
@@ -47,17 +51,20 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     }
     __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < n; e += 32) mx = fmaxf(mx, z[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < n; e += 32) sum += expf(z[e] - mx);
-    sum = warp_sum(sum);
+    float mx = 0.f, sum = 1.f;
+    if (!sigmoid_scores) {
+        mx = -INFINITY;
+        for (int e = lane; e < n; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        sum = 0.f;
+        for (int e = lane; e < n; e += 32) sum += expf(z[e] - mx);
+        sum = warp_sum(sum);
+    }
     __syncwarp();
     for (int e = lane; e < n; e += 32) {
-        const float s = expf(z[e] - mx) / sum;
+        const float s = sigmoid_scores ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum;
         z[e] = s;
-        c[e] = s + correction[e];
+        c[e] = s + (correction != nullptr ? correction[e] : 0.f);
         ok[e] = 0;
         dense[(size_t)t * n + e] = 0.f;
     }
@@ -96,31 +103,41 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
 
 extern "C" int lb_moe_route(const void* h, const float* w_router, const float* correction, float* dense, int* chosen,
                             float* chosen_w, float* id_weight, int tokens, int width, int n, int experts, int top, int groups,
-                            int keep, float scale, int dtype, void* stream) {
+                            int keep, float scale, int sigmoid_scores, int dtype, void* stream) {
     if (tokens <= 0) return kOk;
     if (n <= 0 || experts < 0 || experts > n || top <= 0 || top > n || groups <= 0 || n % groups || keep <= 0 || keep > groups)
         return kBadSize;
     if (n > kRouteMax) return kTooLarge;
     LB_DISPATCH_DTYPE(dtype, moe_route_kernel<T><<<tokens, kRouteWarps * 32, 0, (cudaStream_t)stream>>>(
-        (const T*)h, w_router, correction, dense, chosen, chosen_w, id_weight, tokens, width, n, experts, top, groups, keep, scale));
+        (const T*)h, w_router, correction, dense, chosen, chosen_w, id_weight, tokens, width, n, experts, top, groups, keep, scale, sigmoid_scores));
     return launch_status();
 }
 
-// gu: [T, experts, 2, ff]; y: [T, experts, ff]; dense: [T, n]
+enum : int { kClampedOutput = 0, kSiluInput = 1 };
+
+__device__ __forceinline__ float expert_act(float g, float u, float w, float limit, float act_alpha, int mode) {
+    if (mode == kSiluInput) {
+        const float wg = w * g;
+        return wg / (1.f + expf(-wg)) * (w * u);
+    }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return w * (g / (1.f + expf(-act_alpha * g)) * (u + 1.f));
+}
+
+// gu: [T, experts, 2, ff]; y: [T, experts, ff]; dense: [T, n] (null: weight 1)
 template <typename T>
 __global__ void moe_activation_kernel(const T* __restrict__ gu, const float* __restrict__ dense, T* __restrict__ y,
-                                      int experts, int ff, int n, float limit, float act_alpha) {
+                                      int experts, int ff, int n, float limit, float act_alpha, int mode) {
     const size_t t = blockIdx.z;
     const int e = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= ff) return;
-    const float w = dense[t * n + e];
+    const float w = dense != nullptr ? dense[t * n + e] : 1.f;
     float v = 0.f;
     if (w != 0.f) {
         const T* row = gu + (t * experts + e) * 2 * (size_t)ff;
-        const float g = fminf(to_f32(row[i]), limit);
-        const float u = fminf(fmaxf(to_f32(row[ff + i]), -limit), limit);
-        v = w * (g / (1.f + expf(-act_alpha * g)) * (u + 1.f));
+        v = expert_act(to_f32(row[i]), to_f32(row[ff + i]), w, limit, act_alpha, mode);
     }
     y[(t * experts + e) * (size_t)ff + i] = from_f32<T>(v);
 }
@@ -129,12 +146,12 @@ __global__ void moe_activation_kernel(const T* __restrict__ gu, const float* __r
 // zeros for the experts that were not chosen without reading their products
 __global__ void __launch_bounds__(256) moe_activation_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ dense,
                                                                  __nv_bfloat16* __restrict__ y, int experts, int ff, int n,
-                                                                 float limit, float act_alpha) {
+                                                                 float limit, float act_alpha, int mode) {
     const size_t t = blockIdx.x;
     const int pieces = ff / 8;
     for (int i = threadIdx.x; i < experts * pieces; i += blockDim.x) {
         const int e = i / pieces, pc = i % pieces;
-        const float w = dense[t * n + e];
+        const float w = dense != nullptr ? dense[t * n + e] : 1.f;
         uint4 out = make_uint4(0, 0, 0, 0);
         if (w != 0.f) {
             const __nv_bfloat16* row = gu + (t * experts + e) * 2 * (size_t)ff;
@@ -146,10 +163,15 @@ __global__ void __launch_bounds__(256) moe_activation_vec_kernel(const __nv_bflo
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-                const float g0 = fminf(g.x, limit), g1 = fminf(g.y, limit);
-                const float u0 = fminf(fmaxf(u.x, -limit), limit), u1 = fminf(fmaxf(u.y, -limit), limit);
-                o2[k] = __floats2bfloat162_rn(w * (g0 / (1.f + __expf(-act_alpha * g0)) * (u0 + 1.f)),
-                                              w * (g1 / (1.f + __expf(-act_alpha * g1)) * (u1 + 1.f)));
+                if (mode == kSiluInput) {
+                    const float g0 = w * g.x, g1 = w * g.y;
+                    o2[k] = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * (w * u.x), __fdividef(g1, 1.f + __expf(-g1)) * (w * u.y));
+                } else {
+                    const float g0 = fminf(g.x, limit), g1 = fminf(g.y, limit);
+                    const float u0 = fminf(fmaxf(u.x, -limit), limit), u1 = fminf(fmaxf(u.y, -limit), limit);
+                    o2[k] = __floats2bfloat162_rn(w * (g0 / (1.f + __expf(-act_alpha * g0)) * (u0 + 1.f)),
+                                                  w * (g1 / (1.f + __expf(-act_alpha * g1)) * (u1 + 1.f)));
+                }
             }
         }
         *reinterpret_cast<uint4*>(y + (t * experts + e) * (size_t)ff + pc * 8) = out;
@@ -157,17 +179,17 @@ __global__ void __launch_bounds__(256) moe_activation_vec_kernel(const __nv_bflo
 }
 
 extern "C" int lb_moe_activation(const void* gu, const float* dense, void* y, int tokens, int experts, int ff, int n, float limit,
-                                 float act_alpha, int dtype, void* stream) {
+                                 float act_alpha, int mode, int dtype, void* stream) {
     if (tokens <= 0 || experts <= 0) return kOk;
-    if (ff <= 0 || n < experts || experts > 65535) return kBadSize;
+    if (ff <= 0 || (dense != nullptr && n < experts) || experts > 65535 || (mode != kClampedOutput && mode != kSiluInput)) return kBadSize;
     if (dtype == kBF16 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)y) & 15) == 0) {
         moe_activation_vec_kernel<<<tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, dense, (__nv_bfloat16*)y, experts, ff,
-                                                                          n, limit, act_alpha);
+                                                                          n, limit, act_alpha, mode);
         return launch_status();
     }
     dim3 grid((ff + 127) / 128, experts, tokens);
     LB_DISPATCH_DTYPE(dtype, moe_activation_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
-        (const T*)gu, dense, (T*)y, experts, ff, n, limit, act_alpha));
+        (const T*)gu, dense, (T*)y, experts, ff, n, limit, act_alpha, mode));
     return launch_status();
 }
 

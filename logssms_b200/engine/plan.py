@@ -187,11 +187,12 @@ class StepPlanner:
         tables, mappings = [], []
         for g in groups:
             bt = g.block_table[rows, :P]
-            page_of_token = bt[token_req, positions // ps].astype(np.int64)
+            entry = positions // g.need.every          # a group of block summaries: the entry of the token's block
+            page_of_token = bt[token_req, entry // ps].astype(np.int64)
             if (page_of_token < 0).any():
                 raise AssertionError("a token of this step has no page")
             tables.append(bt)
-            mappings.append(page_of_token * ps + positions % ps)
+            mappings.append(page_of_token * ps + entry % ps)
         # pack -> one pinned buffer -> one copy
         sections = [tokens, positions, token_req, cu, starts, rows, logit_rows]
         for bt, mp in zip(tables, mappings):

@@ -37,4 +37,8 @@ from ..config.dudurax import ARCHITECTURE as _DUDURAX, DuduraxConfig  # noqa: E4
 
 register_architecture(_DUDURAX, DuduraxConfig)
 
+from ..config.kuvazen import ARCHITECTURE as _KUVAZEN, KuvazenConfig  # noqa: E402
+
+register_architecture(_KUVAZEN, KuvazenConfig)
+
 __all__ = ["Architecture", "DecoderModel", "build_model", "register_architecture"]

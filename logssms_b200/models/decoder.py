@@ -26,6 +26,9 @@ class DecoderModel(Part):
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, perturb_init)
         self.lm_head = HEADS.get(spec.lm_head_kind)(spec.vocab_size, spec.hidden_size, spec.lm_head_multiplier,
                                                     self.embedding if spec.tie_word_embeddings else None)
+        # parts that several layers share and whose tensors are stored at the model's root (a second embedding table that
+        # every layer reads a slice of): a layer puts them into `shared["model_parts"]` under their checkpoint prefix
+        self.model_parts = dict(shared.get("model_parts", {}))
         self.schedule = spec.resolved_schedule()
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
@@ -42,6 +45,10 @@ class DecoderModel(Part):
                 self.spec.lm_head_name: self.lm_head}
         for block_spec, block in zip(self.spec.layers, self.layers):
             kids[block_spec.prefix] = block
+        for prefix, part in self.model_parts.items():
+            if prefix in kids:
+                raise ValueError(f"a shared part's prefix {prefix!r} is taken")
+            kids[prefix] = part
         return kids
 
     def duplicate_names(self) -> dict[str, str]:
@@ -106,6 +113,8 @@ class DecoderModel(Part):
             # the one before the head
             ctx.extras["next_norm_takes_scaled"] = getattr(getattr(nxt, "input_norm", None) if nxt is not None else self.final_norm,
                                                            "takes_scaled_rows", False)
+            # ... or, on a 32-bit stream, already normed by that norm (the kernel that closes the block does it on the way)
+            ctx.extras["next_input_norm"] = getattr(nxt, "input_norm", None)
             if PROFILER.nvtx:                      # named ranges per layer (and per part inside it) for a timeline
                 with nvtx_range(f"layer {e.layer}"):
                     x, residual = self.layers[e.layer].forward(x, residual, ctx, e.cache, e.writes_cache)
@@ -115,6 +124,7 @@ class DecoderModel(Part):
                 tap(i, x, residual)
         ctx.extras.pop("next_norm_takes_summed", None)
         ctx.extras.pop("next_norm_takes_scaled", None)
+        ctx.extras.pop("next_input_norm", None)
         return x, residual
 
     def logits(self, x: torch.Tensor, residual, rows: torch.Tensor) -> torch.Tensor:

@@ -121,10 +121,12 @@ class StreamRows:
     """A residual stream that is kept in 32-bit whatever the activation dtype: `f32` [rows, width] is the stream, `act`
     its copy rounded to the activation dtype, which the next sublayer's products read (in a float32 engine both are one
     tensor).  Post-norm blocks hand these from layer to layer; a norm with `takes_stream_rows = True` normalises them."""
-    __slots__ = ("f32", "act")
+    __slots__ = ("f32", "act", "normed_by")
 
-    def __init__(self, f32, act):
-        self.f32, self.act = f32, act
+    def __init__(self, f32, act, normed_by=None):
+        # `normed_by`: on a pre-norm stream `act` may already be the output of the norm that reads the stream next
+        # (the kernel that closed the layer before made it on the way); it then names that norm
+        self.f32, self.act, self.normed_by = f32, act, normed_by
 
     @property
     def shape(self):

@@ -1345,36 +1345,47 @@ def latent_attention_wide(qa: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.
 
 
 # --------------------------------------------------------------------------- routed feed-forward
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, num_experts: int, top: int, groups: int,
-              keep: int, scale: float):
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor | None, num_experts: int, top: int, groups: int,
+              keep: int, scale: float, sigmoid_scores: bool = False):
     """(dense weights float32 [T, n], chosen int32 [T, top], their weights float32 [T, top], identity weight float32 [T]):
-    see `csrc/moe.cu`.  `w_router` float32 [n, width]; outputs num_experts .. n-1 are identity experts."""
+    see `csrc/moe.cu`.  `w_router` float32 [n, width]; outputs num_experts .. n-1 are identity experts.  Scores are the
+    softmax over all outputs, or with `sigmoid_scores` the sigmoid of each; `correction` (may be None) moves the choice only."""
     _cuda(h, w_router, correction)
     T, width = h.shape
     n = w_router.shape[0]
     _need(h.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == width
-          and correction.dtype == torch.float32 and correction.shape == (n,), "router weight float32 [n, width], correction float32 [n]")
+          and (correction is None or (correction.dtype == torch.float32 and correction.shape == (n,))),
+          "router weight float32 [n, width], correction float32 [n]")
     dense = torch.empty((T, n), dtype=torch.float32, device=h.device)
     chosen = torch.empty((T, top), dtype=torch.int32, device=h.device)
     chosen_w = torch.empty((T, top), dtype=torch.float32, device=h.device)
     idw = torch.empty((T,), dtype=torch.float32, device=h.device)
-    f = _fn("moe", "lb_moe_route", [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_void_p])
+    f = _fn("moe", "lb_moe_route", [c_void_p] * 7 + [c_int] * 7 + [c_float, c_int, c_int, c_void_p])
     _check(f(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(idw), T, width, n,
-             num_experts, top, groups, keep, scale, _code(h), _stream()), "moe_route", f"({n} outputs, top {top}, {groups} groups)")
+             num_experts, top, groups, keep, scale, int(sigmoid_scores), _code(h), _stream()), "moe_route",
+           f"({n} outputs, top {top}, {groups} groups)")
     return dense, chosen, chosen_w, idw
 
 
-def moe_activation(gate_up: torch.Tensor, dense: torch.Tensor, num_experts: int, limit: float, act_alpha: float) -> torch.Tensor:
-    """gate_up: [T, experts * 2 * ff] (per expert gate | up); returns [T, experts * ff] with every expert's clamped gated
-    activation times the token's weight for that expert (0 where the expert was not chosen)."""
+EXPERT_MODES = {"clamped": 0, "silu_input": 1}
+
+
+def moe_activation(gate_up: torch.Tensor, dense: torch.Tensor | None, num_experts: int, limit: float, act_alpha: float,
+                   mode: str = "clamped") -> torch.Tensor:
+    """gate_up: [T, experts * 2 * ff] (per expert gate | up); returns [T, experts * ff] with every expert's gated
+    activation and the token's weight for that expert (0 where the expert was not chosen).  Mode "clamped": weight *
+    g~ sigmoid(act_alpha g~) (u~ + 1) with gate and up clamped at `limit`; "silu_input": silu(w g) * (w u), the expert on
+    an input that was multiplied by the weight.  `dense` None: every weight is 1 (a dense gated layer: one expert)."""
     _cuda(gate_up, dense)
     T = gate_up.shape[0]
     ff = gate_up.shape[1] // (2 * num_experts)
     _need(gate_up.is_contiguous() and gate_up.shape[1] == 2 * num_experts * ff, "gate_up must be contiguous [T, experts*2*ff]")
-    _need(dense.dtype == torch.float32 and dense.is_contiguous() and dense.shape[0] == T and dense.shape[1] >= num_experts, "dense weights float32 [T, n]")
+    _need(dense is None or (dense.dtype == torch.float32 and dense.is_contiguous() and dense.shape[0] == T and dense.shape[1] >= num_experts),
+          "dense weights float32 [T, n]")
     y = torch.empty((T, num_experts * ff), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("moe", "lb_moe_activation", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
-    _check(f(_ptr(gate_up), _ptr(dense), _ptr(y), T, num_experts, ff, dense.shape[1], limit, act_alpha, _code(gate_up), _stream()), "moe_activation")
+    f = _fn("moe", "lb_moe_activation", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(dense), _ptr(y), T, num_experts, ff, 0 if dense is None else dense.shape[1], limit, act_alpha,
+             EXPERT_MODES[mode], _code(gate_up), _stream()), "moe_activation")
     return y
 
 
@@ -1394,4 +1405,194 @@ def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty_like(x)
     f = _fn("moe", "lb_gelu_tanh", [c_void_p, c_void_p, c_long, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(out), x.numel(), _code(x), _stream()), "gelu_tanh")
+    return out
+
+
+# --------------------------------------------------------------------------- pre-norm layers on a 32-bit stream
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+
+
+def embed_norm(table: torch.Tensor, ids: torch.Tensor, weight: torch.Tensor, eps: float, kind: str,
+               bad_ids: torch.Tensor | None = None) -> torch.Tensor:
+    """float32 [tokens, width]: norm(table[id]) * weight, the first value of a 32-bit stream."""
+    _cuda(table, ids, weight)
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous(), "embedding table must be a contiguous [vocab, hidden] matrix")
+    V, H = table.shape
+    _need(weight.dtype == torch.float32 and weight.shape == (H,) and weight.is_contiguous(), "norm weight must be float32 [width]")
+    out = torch.empty((ids.numel(), H), dtype=torch.float32, device=table.device)
+    f = _fn("stream_layer", "lb_embed_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p,
+                                              c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(table), _ptr(ids), _ptr(weight), eps, ids.numel(), H, V, NORM_KINDS[kind], _ptr(bad_ids), _code(table),
+             _stream()), "embed_norm", f"(width {H})")
+    return out
+
+
+def stream_add_norm(x: torch.Tensor, y: torch.Tensor | None, channel_scale: torch.Tensor | None, weight: torch.Tensor | None,
+                    eps: float, kind: str, act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """x += channel_scale * y in place (x: the float32 stream; y: activations or None), then norm(x) * weight rounded to
+    `act_dtype` (None without a weight).  Returns (x, normed)."""
+    _cuda(x, y, channel_scale, weight)
+    rows, H = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
+    _need(y is None or (y.shape == x.shape and y.dtype == act_dtype and y.is_contiguous()), "y must match the stream's shape")
+    for v, name in ((channel_scale, "channel_scale"), (weight, "weight")):
+        _need(v is None or (v.dtype == torch.float32 and v.shape == (H,) and v.is_contiguous()), f"{name} must be float32 [width]")
+    _need(y is not None or weight is not None, "nothing to do")
+    h = None if weight is None else torch.empty((rows, H), dtype=act_dtype, device=x.device)
+    f = _fn("stream_layer", "lb_stream_add_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(y), _ptr(channel_scale), _ptr(weight), eps, _ptr(x) if y is not None else None, _ptr(h), rows, H,
+             NORM_KINDS[kind], _DTYPE_CODE[act_dtype], _stream()), "stream_add_norm", f"(width {H})")
+    return x, h
+
+
+def stream_side(x: torch.Tensor, y: torch.Tensor | None, channel_scale: torch.Tensor | None, ids: torch.Tensor,
+                side_table: torch.Tensor, offset: int, gate_w: torch.Tensor, proj_w: torch.Tensor, side_w: torch.Tensor,
+                side_eps: float, next_weight: torch.Tensor | None, next_eps: float, next_kind: str,
+                act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """x += channel_scale * y, then the token's side input x += RMSNorm(proj_w (gelu_tanh(gate_w x) * e)) * side_w with e the
+    columns [offset, offset + dim) of side_table[id], all in place on the float32 stream; with `next_weight` also the
+    norm that reads the stream next, rounded to `act_dtype`.  Returns (x, normed or None)."""
+    _cuda(x, y, channel_scale, ids, side_table, gate_w, proj_w, side_w, next_weight)
+    _i32(ids, "ids")
+    rows, H = x.shape
+    dim = gate_w.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
+    _need(y is None or (y.shape == x.shape and y.dtype == act_dtype and y.is_contiguous()), "y must match the stream's shape")
+    _need(gate_w.shape == (dim, H) and proj_w.shape == (H, dim) and gate_w.is_contiguous() and proj_w.is_contiguous()
+          and gate_w.dtype == proj_w.dtype == side_table.dtype == act_dtype and side_table.dim() == 2 and side_table.is_contiguous(),
+          "side input wants gate [dim, width], proj [width, dim] and a [vocab, columns] table in the activation dtype")
+    for v, name in ((channel_scale, "channel_scale"), (side_w, "side norm weight"), (next_weight, "next norm weight")):
+        _need(v is None or (v.dtype == torch.float32 and v.shape == (H,) and v.is_contiguous()), f"{name} must be float32 [width]")
+    h = None if next_weight is None else torch.empty((rows, H), dtype=act_dtype, device=x.device)
+    f = _fn("stream_layer", "lb_stream_side", [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                                               c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(y), _ptr(channel_scale), _ptr(ids), _ptr(side_table), side_table.shape[1], offset, side_table.shape[0],
+             _ptr(gate_w), _ptr(proj_w), _ptr(side_w), side_eps, dim, _ptr(next_weight), next_eps, NORM_KINDS[next_kind], _ptr(x),
+             _ptr(h), rows, H, _DTYPE_CODE[act_dtype], _stream()), "stream_side", f"(width {H}, side {dim})")
+    return x, h
+
+
+# --------------------------------------------------------------------------- minGRU
+_mingru_chunk = None
+
+
+def mingru_chunk() -> int:
+    """Tokens per chunk of the chunked form (the kernels' constant)."""
+    global _mingru_chunk
+    if _mingru_chunk is None:
+        _mingru_chunk = int(_fn("mingru", "lb_mingru_chunk", [])())
+    return _mingru_chunk
+
+
+def _mingru_checks(proj, bias_z, bias_x, state, W):
+    _cuda(proj, bias_z, bias_x, state)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == 3 * W, "proj must be [tokens, 3 * width] with unit column stride")
+    for b in (bias_z, bias_x):
+        _need(b.dtype == torch.float32 and b.shape == (W,) and b.is_contiguous(), "biases must be float32 [width]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == W and state.is_contiguous(),
+          "the state must be contiguous float32 [slots, width]")
+
+
+def mingru_scan(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+                start_pos: torch.Tensor, slots: torch.Tensor, num_requests: int, width: int,
+                request_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Token by token S <- (1 - z) S + z c over every (listed) request's tokens; returns S * silu(gate) [tokens, width]
+    in proj's dtype.  proj: [tokens, 3 * width] = z | candidate | gate products; state float32 [slots, width]."""
+    _mingru_checks(proj, bias_z, bias_x, state, width)
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots")):
+        _i32(t, name)
+    if out is None:
+        out = torch.empty((proj.shape[0], width), dtype=proj.dtype, device=proj.device)
+    n = num_requests if request_list is None else request_list.numel()
+    f = _fn("mingru", "lb_mingru_scan", [c_void_p, c_long] + [c_void_p] * 8 + [c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots),
+             _ptr(request_list), _ptr(out), n, width, _code(proj), _stream()), "mingru_scan", f"(width {width})")
+    return out
+
+
+def mingru_chunked(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+                   start_pos: torch.Tensor, slots: torch.Tensor, chunks: torch.Tensor, num_chunks: int, per_request: torch.Tensor,
+                   num_long: int, num_requests: int, width: int, out: torch.Tensor) -> torch.Tensor:
+    """The same recurrence over the long portions' chunks side by side (work lists of `StepContext.long_portion_chunks`
+    with chunks of `mingru_chunk()` tokens): three launches.  Writes the rows of the long portions into `out`."""
+    _mingru_checks(proj, bias_z, bias_x, state, width)
+    for t, name in ((cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (slots, "slots"), (chunks, "chunks"), (per_request, "per_request")):
+        _i32(t, name)
+    fold = torch.empty((2, num_chunks, width), dtype=torch.float32, device=proj.device)
+    new_state = torch.empty((num_requests, width), dtype=torch.float32, device=proj.device)
+    f = _fn("mingru", "lb_mingru_chunked", [c_void_p, c_long] + [c_void_p] * 7 + [c_int, c_void_p, c_int] + [c_void_p] * 4 + [c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), _ptr(bias_z), _ptr(bias_x), _ptr(state), _ptr(cu_seqlens), _ptr(start_pos), _ptr(slots),
+             _ptr(chunks), num_chunks, _ptr(per_request), num_long, _ptr(fold[0]), _ptr(fold[1]), _ptr(new_state), _ptr(out), width,
+             _code(proj), _stream()), "mingru_chunked", f"(width {width})", launches=3)
+    return out
+
+
+# --------------------------------------------------------------------------- attention over a window and pooled blocks
+def pooled_prepare(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, positions: torch.Tensor,
+                   slot_mapping: torch.Tensor, qk_table: torch.Tensor, v_table: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """Rotated queries [tokens, heads, head_dim]; rotated keys and values go to the caches at the tokens' slots.  qkv:
+    [tokens, heads*head_dim + kv_heads*head_dim + kv_heads*value_dim].  Tables: float32 [positions, n] (cos | sin of n/2
+    neighbouring pairs); n = 0: no rotation."""
+    _cuda(qkv, positions, slot_mapping, qk_table, v_table, k_cache, v_cache)
+    _i32(positions, "positions"); _i32(slot_mapping, "slot_mapping")
+    T = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim,
+          "qkv must be [tokens, q | k | v] with unit column stride")
+    _need(k_cache.dtype == v_cache.dtype == qkv.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and k_cache.shape[2:] == (num_kv_heads, head_dim) and v_cache.shape[2:] == (num_kv_heads, value_dim), "caches must be [pages, page, kv_heads, dim]")
+    for tb in (qk_table, v_table):
+        _need(tb.dtype == torch.float32 and tb.dim() == 2 and tb.is_contiguous(), "rotation tables must be contiguous float32")
+    rows = max(qk_table.shape[0] if qk_table.shape[1] else 0, v_table.shape[0] if v_table.shape[1] else 0, 1)
+    _need((qk_table.shape[1] == 0 or qk_table.shape[0] == rows) and (v_table.shape[1] == 0 or v_table.shape[0] == rows),
+          "both rotation tables must have a row per position")
+    q = torch.empty((T, num_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("attention_pooled", "lb_pooled_prepare", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                      c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p])
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(positions), _ptr(slot_mapping), _ptr(qk_table), qk_table.shape[1], _ptr(v_table),
+             v_table.shape[1], rows, _ptr(q), _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim, value_dim,
+             int(write_kv), _code(qkv), _stream()), "pooled_prepare")
+    return q
+
+
+def pooled_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
+                  positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, pooled_slots: torch.Tensor,
+                  pool: int) -> None:
+    """Every token of the step that ends a block of `pool` tokens writes the means of the block's cached keys and values
+    to the block's entry (`pooled_slots[t]`) of the pooled caches."""
+    _cuda(k_cache, v_cache, kp_cache, vp_cache, positions, token_req, block_table, pooled_slots)
+    for t, name in ((positions, "positions"), (token_req, "token_req"), (block_table, "block_table"), (pooled_slots, "pooled_slots")):
+        _i32(t, name)
+    _need(kp_cache.shape[2:] == k_cache.shape[2:] and vp_cache.shape[2:] == v_cache.shape[2:] and kp_cache.dtype == k_cache.dtype
+          and kp_cache.is_contiguous() and vp_cache.is_contiguous(), "pooled caches must have the token caches' entry shapes")
+    G, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    f = _fn("attention_pooled", "lb_pooled_blocks", [c_void_p] * 7 + [c_int, c_void_p] + [c_int] * 7 + [c_void_p])
+    _check(f(_ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(positions), _ptr(token_req), _ptr(block_table),
+             block_table.shape[1], _ptr(pooled_slots), positions.numel(), G, dim, vdim, k_cache.shape[1], pool, _code(k_cache), _stream()),
+           "pooled_blocks")
+
+
+def pooled_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
+                     block_table: torch.Tensor, pooled_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                     v_table: torch.Tensor, scale: float, window: int, pool: int, token_list: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """[tokens, heads * value_dim]: attention of every (listed) token over its window's tokens and the pooled blocks
+    behind it, a warp per (token, head), everything in float32; the summed values are turned back by the query's position."""
+    _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, token_req, positions, v_table, token_list)
+    for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, name)
+    T, H, dim = q.shape
+    G, vdim = v_cache.shape[2], v_cache.shape[3]
+    _need(q.is_contiguous() and q.dtype == k_cache.dtype, "queries must be contiguous [tokens, heads, dim] in the cache's dtype")
+    if out is None:
+        out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+    n = T if token_list is None else token_list.numel()
+    f = _fn("attention_pooled", "lb_pooled_attention", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                        c_void_p, c_int, c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(pooled_table), pooled_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
+             v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _code(q),
+             _stream()), "pooled_attention", f"(dim {dim}, value dim {vdim})")
     return out

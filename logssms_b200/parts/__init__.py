@@ -1,17 +1,20 @@
 from .base import MATRIX, TABLE, VECTOR, ParamSpec, Part
 from .context import Runtime, StepContext
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .rope import RotaryEmbedding, inverse_frequencies
 from .attention import Attention
 from .mamba2 import Mamba2
 from .mlp import GatedMLP
 from .gla import GatedLinearAttention
 from .latent_attention import LatentAttention
-from .moe import DenseMLP, RoutedMLP
-from .embedding import BareLMHead, Embedding, LMHead, PairEmbedding
-from .block import PostNormBlock, PreNormParallelBlock
+from .moe import ClampedGLU, DenseMLP, RoutedMLP
+from .mingru import MinGRU
+from .pooled_attention import PooledWindowAttention
+from .embedding import BareLMHead, Embedding, LMHead, NormedEmbedding, PairEmbedding
+from .block import PostNormBlock, PreNormParallelBlock, PreNormStreamBlock, TokenSideInput
 
 __all__ = ["MATRIX", "TABLE", "VECTOR", "ParamSpec", "Part", "Runtime", "StepContext", "RMSNorm",
            "RotaryEmbedding", "inverse_frequencies", "Attention", "Mamba2", "GatedMLP", "Embedding", "LMHead",
            "PreNormParallelBlock", "PostNormBlock", "GatedLinearAttention", "LatentAttention", "DenseMLP", "RoutedMLP",
-           "PairEmbedding", "BareLMHead"]
+           "PairEmbedding", "BareLMHead", "LayerNorm", "MinGRU", "PooledWindowAttention", "ClampedGLU", "NormedEmbedding",
+           "PreNormStreamBlock", "TokenSideInput"]

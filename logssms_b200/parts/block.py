@@ -200,3 +200,151 @@ class PostNormBlock(Part):
             else:
                 x = self.ff_norm.post(x, y, skip)
         return x, None
+
+
+class SharedTable(Part):
+    """A table stored once at the model's root that several layers read (each a slice of every row)."""
+
+    def __init__(self, name: str, shape: tuple[int, int], std: float = 1.0):
+        self.name, self.shape, self.std = name, tuple(shape), std
+        self.table: torch.Tensor | None = None
+
+    def param_specs(self):
+        from .base import MATRIX, ParamSpec, normal_init
+        return {self.name: ParamSpec(self.shape, MATRIX, normal_init(self.std))}
+
+    def bind(self, t):
+        self.table = t[self.name]
+
+
+class TokenSideInput(Part):
+    """A layer's input from the token itself: x <- x + RMSNorm(proj (gelu_tanh(gate x) * e)) * norm, where e are this
+    layer's `dim` columns of the token's row of a side table that all layers share (one tensor at the model's root).
+    It runs inside the kernel that closes the layer (`K.stream_side`).  Tensors: gate [dim, width], proj [width, dim],
+    norm [width]; the table under `spec.table_name`."""
+    kernels = ("stream_layer",)
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        from .base import MATRIX, VECTOR, ParamSpec, normal_init, ones_init
+        self.spec = spec
+        self._specs = {"gate": ParamSpec((spec.dim, spec.hidden_size), MATRIX, normal_init(spec.hidden_size ** -0.5)),
+                       "proj": ParamSpec((spec.hidden_size, spec.dim), MATRIX, normal_init(spec.dim ** -0.5)),
+                       "norm": ParamSpec((spec.hidden_size,), VECTOR, ones_init(0.1 if perturb_init else 0.0))}
+        prefix, _, name = spec.table_name.rpartition(".")
+        prefix = prefix + "." if prefix else ""
+        parts = shared.setdefault("model_parts", {}) if shared is not None else {}
+        table = parts.get(prefix)
+        if table is None:
+            table = parts[prefix] = SharedTable(name, (spec.vocab_size, spec.table_width))
+        elif not isinstance(table, SharedTable) or table.name != name or table.shape != (spec.vocab_size, spec.table_width):
+            raise ValueError(f"the layers disagree on the side table {spec.table_name!r}")
+        self.shared_table = table
+        self.gate = self.proj = self.norm = None
+
+    def param_specs(self):
+        return dict(self._specs)
+
+    def bind(self, t):
+        self.gate, self.proj, self.norm = t["gate"], t["proj"], t["norm"]
+
+    def close(self, x_f32, y, channel_scale, ids, next_norm, act_dtype):
+        """x += channel_scale * y (y may be None), the side input, and the norm that follows; (x, normed or None)."""
+        s = self.spec
+        nw, neps, nkind = (None, 0.0, "layernorm") if next_norm is None else (next_norm.weight, next_norm.eps, next_norm.norm_kind)
+        return K.stream_side(x_f32, y, channel_scale, ids, self.shared_table.table, s.offset, self.gate, self.proj, self.norm,
+                             s.eps, nw, neps, nkind, act_dtype)
+
+
+@BLOCKS.register("prenorm_stream")
+class PreNormStreamBlock(Part):
+    """Pre-norm block on a 32-bit stream (`K.StreamRows`): x <- x + s1 * mixer(norm1(x)); with a feed-forward
+    x <- x + s2 * ff(norm2(x)); with a side input x <- x + side(x, token).  s1, s2 are stored scales per channel
+    (`layer_scale`).  Every sum and norm is 32-bit; the sublayers read the normed rows in the activation dtype.
+
+    Three kernels besides the sublayers' own: the mixer's output joins the stream and norm2 reads it in one
+    (`K.stream_add_norm`); the feed-forward's output joins, the side input is added and the NEXT block's first norm
+    reads the result in one (`K.stream_side`); norm1 runs alone only where the block before could not do it."""
+
+    def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
+        self.spec = spec
+        m = spec.mixer
+        if m.in_scale != 1.0 or m.out_scale != 1.0:
+            raise ValueError("prenorm_stream blocks take a mixer without input or output multipliers")
+        self.mixer = MIXERS.get(m.spec.kind)(m.spec, perturb_init=perturb_init, shared=shared)
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, perturb_init)
+        self.feed_forward = self.ff_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, perturb_init=perturb_init,
+                                                                          shared=shared)
+            self.ff_norm = NORMS.get(spec.feed_forward_norm.kind)(spec.feed_forward_norm, perturb_init)
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "norm_kind"):
+                raise ValueError("prenorm_stream blocks need norms with a form on a 32-bit stream (`norm_kind`)")
+        self.side = None if spec.side is None else TokenSideInput(spec.side, perturb_init, shared)
+        self._jitter = 0.3 if perturb_init else 0.0
+        self.scale_mixer = self.scale_ff = None
+
+    @property
+    def input_norm(self):
+        return self.mixer_norm
+
+    def param_specs(self):
+        from .base import VECTOR, ParamSpec, ones_init
+        if not self.spec.layer_scale:
+            return {}
+        H = self.spec.mixer_norm.size
+        names = self.spec.layer_scale_names[:2 if self.feed_forward is not None else 1]
+        return {n: ParamSpec((H,), VECTOR, ones_init(self._jitter)) for n in names}
+
+    def bind(self, t):
+        names = self.spec.layer_scale_names
+        self.scale_mixer, self.scale_ff = t.get(names[0]), t.get(names[1])
+
+    def children(self):
+        s = self.spec
+        kids = {s.mixer_norm_name: self.mixer_norm, s.mixer.name: self.mixer}
+        if self.feed_forward is not None:
+            kids[s.feed_forward_norm_name] = self.ff_norm
+            kids[s.feed_forward_name] = self.feed_forward
+        if self.side is not None:
+            kids[s.side_name] = self.side
+        return kids
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def setup(self, rt) -> None:
+        self.mixer.setup(rt)
+        if self.feed_forward is not None:
+            self.feed_forward.setup(rt)
+
+    def forward(self, x, residual, ctx, cache_layer: int, writes_cache: bool = True):
+        if not isinstance(x, K.StreamRows) or residual is not None:
+            raise ValueError("a prenorm_stream block takes a 32-bit stream (`StreamRows`), as its embedding or the block before leaves it")
+        act = x.act.dtype
+        stream = x.f32
+        if x.normed_by is self.mixer_norm:
+            h = x.act
+        else:
+            _, h = K.stream_add_norm(stream, None, None, self.mixer_norm.weight, self.mixer_norm.eps, self.mixer_norm.norm_kind, act)
+        with nvtx_range(self.spec.mixer.spec.kind):
+            y = self.mixer.forward(h, ctx, cache_layer, writes_cache)
+        scale, y_scale = self.scale_mixer, None
+        if self.feed_forward is not None:
+            _, h = K.stream_add_norm(stream, y, scale, self.ff_norm.weight, self.ff_norm.eps, self.ff_norm.norm_kind, act)
+            with nvtx_range(self.spec.feed_forward.kind):
+                y = self.feed_forward.forward(h)
+            scale = self.scale_ff
+        # what is left to join the stream (y with its scale) joins in the kernel that closes the block
+        nxt = ctx.extras.get("next_input_norm")
+        nxt = nxt if hasattr(nxt, "norm_kind") else None
+        if self.side is not None:
+            _, h = self.side.close(stream, y, scale, ctx.token_ids, nxt, act)
+        elif nxt is not None:
+            _, h = K.stream_add_norm(stream, y, scale, nxt.weight, nxt.eps, nxt.norm_kind, act)
+        else:
+            K.stream_add_norm(stream, y, scale, None, 0.0, "layernorm", act)
+            h = None
+        if h is None:
+            return K.StreamRows(stream, x.act[:0]), None
+        return K.StreamRows(stream, h, normed_by=nxt), None

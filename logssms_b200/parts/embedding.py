@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from ..registry import EMBEDDINGS, HEADS
+from ..registry import EMBEDDINGS, HEADS, NORMS
 from .base import MATRIX, ParamSpec, Part, normal_init
 
 
@@ -62,6 +62,36 @@ class PairEmbedding(Part):
         state = ctx.cache.states[cache_layer]["previous_token"]
         return K.embed_pair(self.weight, self.pairs, ids, ctx.token_req, ctx.cu_seqlens, ctx.start_pos, ctx.slots, state,
                             self.multiplier, self.buckets, self.mul_prev, self.mul_cur, self.bad_ids)
+
+
+@EMBEDDINGS.register("normed_embedding")
+class NormedEmbedding(Part):
+    """The token's row of the table, normed (the norm of `norm`, a `NormSpec`, with its own weight): the first value of a
+    32-bit stream (`K.StreamRows`).  Tensors: `embed` and the norm's weight."""
+    kernels = ("embed", "stream_layer")
+
+    def __init__(self, vocab_size: int, hidden_size: int, multiplier: float = 1.0, *, norm):
+        if multiplier != 1.0:
+            raise ValueError("a normed embedding has no multiplier (the norm would undo it)")
+        self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.norm = NORMS.get(norm.kind)(norm)
+        if not hasattr(self.norm, "norm_kind"):
+            raise ValueError(f"norm {norm.kind!r} has no form on a 32-bit stream")
+        self.weight = self.bad_ids = None
+
+    def param_specs(self):
+        return {"embed": ParamSpec((self.vocab_size, self.hidden_size), MATRIX, normal_init(1.0))}
+
+    def children(self):
+        return {"": self.norm}
+
+    def bind(self, t):
+        self.weight = t["embed"]
+        self.bad_ids = torch.zeros(1, dtype=torch.int32, device=self.weight.device)
+
+    def forward(self, ids: torch.Tensor):
+        x = K.embed_norm(self.weight, ids, self.norm.weight, self.norm.eps, self.norm.norm_kind, self.bad_ids)
+        return K.StreamRows(x, x.new_empty((0, self.hidden_size), dtype=self.weight.dtype))
 
 
 @HEADS.register("lm_head")

@@ -17,6 +17,7 @@ class RMSNorm(Part):
     takes_summed_rows = True  # forward() takes `K.SummedRows` as x: the product before has joined the residual already
     takes_scaled_rows = True  # forward() takes `K.ScaledRows` as x: it applies the pending multiplier while it loads x
     takes_stream_rows = True  # forward() takes `K.StreamRows` as x (a 32-bit stream); `post()` is the post-norm form
+    norm_kind = "rmsnorm"     # what the kernels of a pre-norm stream call this norm (`K.NORM_KINDS`)
     kernels = ("norm", "linear_skinny", "stream_norm")
 
     def __init__(self, spec, perturb_init: bool = False):
@@ -66,3 +67,31 @@ class RMSNorm(Part):
             return outs, shared["residual_out"]
         return K.add_rmsnorm(x, self.weight, self.eps, residual, other=other, in_scales=in_scales,
                              out_scales=out_scales, want_residual=want_residual)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Part):
+    """(x - mean) / sqrt(variance + eps) * weight, no bias; the variance is the mean of the squared deviations.  It reads a
+    32-bit stream (`K.StreamRows`) and hands the normed rows on in the activation dtype; the blocks of a pre-norm stream
+    fuse it into the kernel that closes the sublayer before (`K.stream_add_norm`, `K.stream_side`), by `norm_kind`."""
+    takes_stream_rows = True
+    norm_kind = "layernorm"
+    kernels = ("stream_layer",)
+
+    def __init__(self, spec, perturb_init: bool = False):
+        self.size, self.eps = spec.size, spec.eps
+        self.param_name = getattr(spec, "param_name", "weight")
+        self._jitter = 0.1 if perturb_init else 0.0
+        self.weight: torch.Tensor | None = None
+
+    def param_specs(self):
+        return {self.param_name: ParamSpec((self.size,), VECTOR, ones_init(self._jitter))}
+
+    def bind(self, t):
+        self.weight = t[self.param_name]
+
+    def forward(self, x, residual=None, *, out_scales=(1.0,), want_residual=True, **unused):
+        if not isinstance(x, K.StreamRows) or residual is not None:
+            raise ValueError("layernorm reads a 32-bit stream (`StreamRows`)")
+        _, normed = K.stream_add_norm(x.f32, None, None, self.weight, self.eps, self.norm_kind, x.act.dtype)
+        return tuple(normed if s == 1.0 else K.scale(normed, s) for s in out_scales), None
