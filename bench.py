@@ -763,6 +763,30 @@ DESIGN_SIZES = {
 }
 
 
+def _kuvazen_config(width: int, layers: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, window: int, pool: int,
+                    gru_width: int, experts: int, top: int, expert_ff: int, dense_ff: int, side: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: attention over a window and pooled blocks and minGRU layers in turn,
+    routed feed-forwards with one dense one in front, a side input per layer."""
+    attention = {"type": "attention",
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": value_dim, "mask": {"size": window, "pool": pool},
+                           "rot": {"base": 10000.0, "dims": key_dim}, "scale": key_dim ** -0.5}}
+    gru = {"type": "mingru", "mixer": {"width": gru_width}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    out = []
+    for i in range(layers):
+        out.append({**(gru if i % 2 else attention), "mlp": {"kind": "dense", "ff": dense_ff, "limit": 7.0} if i == 0 else moe})
+    return {"architecture": "Kuvazen", "layers": out, "norm": {"eps": 1e-5}, "token_side": {"dim": side}, "vocab": vocab, "width": width}
+
+
+# Kuvazen beside Dudurax (the closest existing model: a 32-bit stream, windowed attention beside a recurrent mixer, routed
+# feed-forwards computed over all experts) at the same width, depth, vocabulary, expert and dense sizes
+KUVAZEN_SIZES = {
+    "w1024": (_kuvazen_config(1024, 4, 8, 2, 64, 128, 1024, 16, 2048, 8, 2, 1024, 2048, 64, 32768), DESIGN_SIZES["w1024"][0]),
+    "w2048": (_kuvazen_config(2048, 4, 16, 4, 128, 128, 2048, 16, 4096, 16, 4, 1408, 8192, 64, 65536), DESIGN_SIZES["w2048"][0]),
+}
+DESIGNS = {"dudurax": (DESIGN_SIZES, "falcon_h1"), "kuvazen": (KUVAZEN_SIZES, "dudurax")}
+
+
 def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: int) -> dict:
     """Prefill (one prompt of PREFILL_TOKENS as one step) and decode (batch x one token from `context`-token contexts) of
     one random-weights model through `Engine.step`, timed with CUDA events after W warm-up steps; then the same steps
@@ -832,16 +856,18 @@ def _design_point(cfg: dict, vocab: int, K: int, W: int, batch: int, context: in
 
 
 def run_design(args) -> dict:
-    """`--design dudurax`: the Dudurax design at a few layer sizes beside Falcon-H1 at the same width and depth."""
+    """`--design NAME`: that design at a few layer sizes beside the closest existing model at the same width and depth
+    (Dudurax beside Falcon-H1, Kuvazen beside Dudurax)."""
+    table, beside = DESIGNS[args.design]
     sizes = {}
-    for name, (new, closest) in DESIGN_SIZES.items():
-        log(f"design sizes {name}: dudurax")
+    for name, (new, closest) in table.items():
+        log(f"design sizes {name}: {args.design}")
         ours = _design_point(new, new["vocab"], args.steps, args.warmup, args.batch, CONTEXT)
-        log(f"design sizes {name}: falcon-h1")
-        base = _design_point(closest, closest["vocab_size"], args.steps, args.warmup, args.batch, CONTEXT)
-        sizes[name] = {"dudurax": ours, "falcon_h1": base, "layers": len(new["layers"]), "width": new["width"]}
+        log(f"design sizes {name}: {beside}")
+        base = _design_point(closest, closest.get("vocab") or closest["vocab_size"], args.steps, args.warmup, args.batch, CONTEXT)
+        sizes[name] = {args.design: ours, beside: base, "layers": len(new["layers"]), "width": new["width"]}
     pk, src = peaks()
-    return {"design": "dudurax", "beside": "falcon_h1", "dtype": "bf16", "data": "synthetic", "peaks": {**pk, "source": src},
+    return {"design": args.design, "beside": beside, "dtype": "bf16", "data": "synthetic", "peaks": {**pk, "source": src},
             "timing": "CUDA events around Engine.step, median; L2 flushed between steps", "sizes": sizes}
 
 
@@ -892,7 +918,7 @@ def main() -> int:
     ap.add_argument("--reference-timeout", type=int, default=900, help="seconds the reference arm may take")
     ap.add_argument("--probe", choices=["decode", "prefill", "mixed"], default=None,
                     help="a short run of one kind of step for a profiler (see profiles/); prints no benchmark line")
-    ap.add_argument("--design", choices=["dudurax"], default=None,
+    ap.add_argument("--design", choices=["dudurax", "kuvazen"], default=None,
                     help="prefill and decode of another design at a few layer sizes beside the closest existing model "
                          "(one JSON line of its own; the default workload is untouched)")
     args = ap.parse_args()

@@ -16,8 +16,9 @@
 //                    block's entry of a second paged cache (one entry per `pool` tokens)
 //   pooled_attention      : a warp per (token, head); a lane scores one key at a time, the lanes share the value
 //                           columns; scores, softmax and sums in float32 (every dtype, every size, every step)
-//   pooled_attention_tile : a CTA per (run of up to 16 neighbouring tokens of a request, kv head): the keys the run's
-//                           queries see are staged through shared memory once for all queries of the group
+//   pooled_attention_tile : bfloat16 prompt portions on the tensor cores: a CTA per (run of up to 64 neighbouring tokens
+//                           of a request, query head); the keys the run sees go through shared memory once for all
+//                           its queries (described at the kernel)
 #include "lb200/common.cuh"
 using namespace lb200;
 
@@ -236,4 +237,260 @@ extern "C" int lb_pooled_attention(const void* q, const void* k_cache, const voi
         pooled_table, pooled_width, token_req, positions, token_list, v_table, v_rot, table_rows, (T*)out, Hq, Hkv, dim, vdim,
         page_size, scale, window, pool));
     return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------ prompt portions on the tensor cores
+// A CTA takes one query head and a run of up to kTileQ neighbouring tokens of one request (four warps of 16 query rows).
+// The keys the run sees - the pooled blocks behind the LAST query's window, then the tokens from the FIRST query's
+// window to the last query - go through shared memory in chunks of kTileK, each row masked per query.  S = Q K^T and
+// P V are `mma.sync` m16n8k16 products of bfloat16 operands with float32 accumulators; scores, maxima, weights and
+// sums are float32.  A weight p enters P V as the two bfloat16 terms hi = bf16(p), lo = bf16(p - hi) (two products
+// into the same accumulator), so it is applied to 16 bits and more, not rounded to 8.
+constexpr int kTileQ = 64, kTileK = 64, kTileThreads = 128;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// grid (tiles, Hq); tiles: int32 [n, 2] (request, first token of the run within its portion), request -1: no work
+template <int kDimSteps, int kValueTiles>
+__global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
+        const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+        const __nv_bfloat16* __restrict__ kp_cache, const __nv_bfloat16* __restrict__ vp_cache, const int* __restrict__ block_table,
+        int table_width, const int* __restrict__ pooled_table, int pooled_width, const int* __restrict__ cu,
+        const int* __restrict__ start_pos, const int* __restrict__ tiles, const float* __restrict__ v_table, int v_rot,
+        int table_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale,
+        int window, int pool) {
+    extern __shared__ __align__(16) unsigned char tile_smem[];
+    const int b = tiles[2 * blockIdx.x];
+    if (b < 0) return;
+    const int t0 = tiles[2 * blockIdx.x + 1];
+    const int head = blockIdx.y, g = head / (Hq / Hkv);
+    const int n_q = min(kTileQ, cu[b + 1] - cu[b] - t0);
+    const int row0 = cu[b] + t0, pos0 = start_pos[b] + t0;
+    const int i_last = pos0 + n_q - 1;
+    const int first = max(0, pos0 - window + 1);                    // the oldest token any query of the run sees
+    const int blocks = max(0, (i_last - window + 1) / pool);        // the blocks the last query sees
+    const int keys = blocks + (i_last - first + 1);
+    const int k_stride = dim + 8, v_stride = vdim + 8;              // elements; the pad staggers the banks
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(tile_smem);
+    __nv_bfloat16* Vs = Ks + kTileK * k_stride;
+    long* rows_s = reinterpret_cast<long*>(Vs + kTileK * v_stride);  // cache row of every key of the chunk (-1: none)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+    const int dsteps = dim / 16, vtiles = vdim / 8;
+    const int* pages = block_table + (size_t)b * table_width;
+    const int* pooled_pages = pooled_table + (size_t)b * pooled_width;
+
+    // this thread's two query rows and their A fragments
+    const int r_lo = warp * 16 + gq, r_hi = r_lo + 8;
+    const int i_lo = pos0 + r_lo, i_hi = pos0 + r_hi;
+    uint32_t qa[kDimSteps][4];
+#pragma unroll
+    for (int ks = 0; ks < kDimSteps; ++ks) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) qa[ks][x] = 0u;
+        if (ks < dsteps) {
+            const int c = ks * 16 + 2 * tq;
+            if (r_lo < n_q) {
+                const __nv_bfloat16* qr = q + ((size_t)(row0 + r_lo) * Hq + head) * dim;
+                qa[ks][0] = *reinterpret_cast<const uint32_t*>(qr + c);
+                qa[ks][2] = *reinterpret_cast<const uint32_t*>(qr + c + 8);
+            }
+            if (r_hi < n_q) {
+                const __nv_bfloat16* qr = q + ((size_t)(row0 + r_hi) * Hq + head) * dim;
+                qa[ks][1] = *reinterpret_cast<const uint32_t*>(qr + c);
+                qa[ks][3] = *reinterpret_cast<const uint32_t*>(qr + c + 8);
+            }
+        }
+    }
+    const int nb_lo = max(0, (i_lo - window + 1) / pool), nb_hi = max(0, (i_hi - window + 1) / pool);
+    // what the warp's 16 rows can see at all: a chunk wholly outside is skipped
+    const int iw0 = pos0 + warp * 16, iw1 = min(iw0 + 15, i_last);
+    const int nb_warp = max(0, (iw1 - window + 1) / pool);
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    float o[kValueTiles][4];
+#pragma unroll
+    for (int n = 0; n < kValueTiles; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    for (int k0 = 0; k0 < keys; k0 += kTileK) {
+        __syncthreads();                                             // the chunk before is consumed
+        if (threadIdx.x < kTileK) {
+            const int kk = k0 + threadIdx.x;
+            long row = -1;
+            if (kk < keys) {
+                bool pooled;
+                row = key_row(kk, blocks, first, pages, pooled_pages, page_size, pooled);
+            }
+            rows_s[threadIdx.x] = row;
+        }
+        __syncthreads();
+        {
+            const int kpieces = dim / 8, vpieces = vdim / 8;
+            for (int idx = threadIdx.x; idx < kTileK * (kpieces + vpieces); idx += kTileThreads) {
+                const int r = idx / (kpieces + vpieces), pc = idx % (kpieces + vpieces);
+                const long row = rows_s[r];
+                const bool pooled = (k0 + r) < blocks;
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (pc < kpieces) {
+                    if (row >= 0) val = *reinterpret_cast<const uint4*>((pooled ? kp_cache : k_cache) + ((size_t)row * Hkv + g) * dim + pc * 8);
+                    *reinterpret_cast<uint4*>(Ks + r * k_stride + pc * 8) = val;
+                } else {
+                    if (row >= 0) val = *reinterpret_cast<const uint4*>((pooled ? vp_cache : v_cache) + ((size_t)row * Hkv + g) * vdim + (pc - kpieces) * 8);
+                    *reinterpret_cast<uint4*>(Vs + r * v_stride + (pc - kpieces) * 8) = val;
+                }
+            }
+        }
+        __syncthreads();
+        // is any key of the chunk visible to any row of this warp?
+        {
+            bool any = false;
+            const int c_last = min(k0 + kTileK, keys) - 1;
+            if (k0 < blocks && k0 < nb_warp) any = true;
+            if (c_last >= blocks) {
+                const int ja = first + max(k0, blocks) - blocks, jb = first + c_last - blocks;
+                if (jb > iw0 - window && ja <= iw1) any = true;
+            }
+            if (!any || iw0 > i_last) continue;
+        }
+        // S = Q K^T
+        float sc[kTileK / 8][4];
+#pragma unroll
+        for (int n = 0; n < kTileK / 8; ++n) {
+            sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+            const __nv_bfloat16* kr = Ks + (n * 8 + gq) * k_stride + 2 * tq;
+#pragma unroll
+            for (int ks = 0; ks < kDimSteps; ++ks)
+                if (ks < dsteps)
+                    mma_bf16(sc[n], qa[ks], *reinterpret_cast<const uint32_t*>(kr + ks * 16), *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8));
+        }
+        // mask, scale, running maxima
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < kTileK / 8; ++n) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int kk = k0 + n * 8 + 2 * tq + (x & 1);
+                const bool hi = x >= 2;
+                const int i = hi ? i_hi : i_lo;
+                bool seen = kk < keys && (hi ? r_hi : r_lo) < n_q;
+                if (seen) {
+                    if (kk < blocks) seen = kk < (hi ? nb_hi : nb_lo);
+                    else { const int j = first + kk - blocks; seen = j <= i && j > i - window; }
+                }
+                const float v = seen ? sc[n][x] * scale : -INFINITY;
+                sc[n][x] = v;
+                if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float c_lo = (m_lo == -INFINITY) ? 0.f : expf(m_lo - mn_lo), c_hi = (m_hi == -INFINITY) ? 0.f : expf(m_hi - mn_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        float s_lo = 0.f, s_hi = 0.f;
+#pragma unroll
+        for (int n = 0; n < kTileK / 8; ++n) {
+            sc[n][0] = (sc[n][0] == -INFINITY) ? 0.f : expf(sc[n][0] - mn_lo);
+            sc[n][1] = (sc[n][1] == -INFINITY) ? 0.f : expf(sc[n][1] - mn_lo);
+            sc[n][2] = (sc[n][2] == -INFINITY) ? 0.f : expf(sc[n][2] - mn_hi);
+            sc[n][3] = (sc[n][3] == -INFINITY) ? 0.f : expf(sc[n][3] - mn_hi);
+            s_lo += sc[n][0] + sc[n][1];
+            s_hi += sc[n][2] + sc[n][3];
+        }
+        s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 1); s_lo += __shfl_xor_sync(0xffffffffu, s_lo, 2);
+        s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 1); s_hi += __shfl_xor_sync(0xffffffffu, s_hi, 2);
+        l_lo = l_lo * c_lo + s_lo;
+        l_hi = l_hi * c_hi + s_hi;
+#pragma unroll
+        for (int n = 0; n < kValueTiles; ++n) { o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi; }
+        // O += P V, P in two bfloat16 terms
+#pragma unroll
+        for (int kstep = 0; kstep < kTileK / 16; ++kstep) {
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float a = sc[2 * kstep + (x >> 1)][(x & 1) * 2], c = sc[2 * kstep + (x >> 1)][(x & 1) * 2 + 1];
+                const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+                ph[x] = pack_bf16(ah, ch);
+                pl[x] = pack_bf16(a - ah, c - ch);
+            }
+            const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(Vs + (kstep * 16 + (lane & 15)) * v_stride);
+#pragma unroll
+            for (int n = 0; n < kValueTiles; ++n) {
+                if (n < vtiles) {
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(v_addr + n * 16));
+                    mma_bf16(o[n], ph, b0, b1);
+                    mma_bf16(o[n], pl, b0, b1);
+                }
+            }
+        }
+    }
+    // weights' sums, the turn back by the query's position, the store
+    const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+    const int half = v_rot >> 1;
+    const float* cs_lo = v_table + (size_t)min(max(i_lo, 0), table_rows - 1) * v_rot;
+    const float* cs_hi = v_table + (size_t)min(max(i_hi, 0), table_rows - 1) * v_rot;
+#pragma unroll
+    for (int n = 0; n < kValueTiles; ++n) {
+        if (n >= vtiles) continue;
+        const int c = n * 8 + 2 * tq;
+        if (r_lo < n_q) {
+            float u = o[n][0] * inv_lo, v = o[n][1] * inv_lo;
+            if (c < v_rot) { const float co = cs_lo[c >> 1], si = cs_lo[half + (c >> 1)]; const float u2 = u * co + v * si; v = v * co - u * si; u = u2; }
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_lo) * Hq + head) * vdim + c) = pack_bf16(u, v);
+        }
+        if (r_hi < n_q) {
+            float u = o[n][2] * inv_hi, v = o[n][3] * inv_hi;
+            if (c < v_rot) { const float co = cs_hi[c >> 1], si = cs_hi[half + (c >> 1)]; const float u2 = u * co + v * si; v = v * co - u * si; u = u2; }
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_hi) * Hq + head) * vdim + c) = pack_bf16(u, v);
+        }
+    }
+}
+
+template <int kDimSteps, int kValueTiles>
+static int launch_tile(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache, const void* vp_cache,
+                       const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* cu,
+                       const int* start_pos, const int* tiles, int num_tiles, const float* v_table, int v_rot, int table_rows,
+                       void* out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, void* stream) {
+    const size_t smem = (size_t)kTileK * ((dim + 8) + (vdim + 8)) * sizeof(__nv_bfloat16) + kTileK * sizeof(long);
+    static size_t have = 0;
+    ensure_dynamic_smem(pooled_attention_tile_kernel<kDimSteps, kValueTiles>, smem, have);
+    dim3 grid(num_tiles, Hq);
+    pooled_attention_tile_kernel<kDimSteps, kValueTiles><<<grid, kTileThreads, smem, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (const __nv_bfloat16*)kp_cache,
+        (const __nv_bfloat16*)vp_cache, block_table, table_width, pooled_table, pooled_width, cu, start_pos, tiles, v_table, v_rot,
+        table_rows, (__nv_bfloat16*)out, Hq, Hkv, dim, vdim, page_size, scale, window, pool);
+    return launch_status();
+}
+
+extern "C" int lb_pooled_attention_tile_q() { return kTileQ; }
+
+// bfloat16 only; dim a multiple of 16 up to 128, vdim a multiple of 8 up to 128, an even v_rot
+extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache,
+                                        const void* vp_cache, const int* block_table, int table_width, const int* pooled_table,
+                                        int pooled_width, const int* cu, const int* start_pos, const int* tiles, int num_tiles,
+                                        const float* v_table, int v_rot, int table_rows, void* out, int Hq, int Hkv, int dim,
+                                        int vdim, int page_size, float scale, int window, int pool, void* stream) {
+    if (num_tiles <= 0) return kOk;
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq > 65535 || dim <= 0 || dim % 16 || vdim <= 0 || vdim % 8 || page_size <= 0 || window <= 0
+        || pool <= 0 || (v_rot & 1) || v_rot > vdim || table_rows <= 0)
+        return kBadSize;
+    if (dim > 128 || vdim > 128) return kTooLarge;
+#define LB_TILE(DS, VT) return launch_tile<DS, VT>(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, pooled_table, \
+        pooled_width, cu, start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, stream)
+    const int ds = dim / 16, vt = vdim / 8;
+    if (ds <= 2) { if (vt <= 4) LB_TILE(2, 4); if (vt <= 8) LB_TILE(2, 8); if (vt <= 12) LB_TILE(2, 12); LB_TILE(2, 16); }
+    if (ds <= 4) { if (vt <= 4) LB_TILE(4, 4); if (vt <= 8) LB_TILE(4, 8); if (vt <= 12) LB_TILE(4, 12); LB_TILE(4, 16); }
+    if (vt <= 4) LB_TILE(8, 4);
+    if (vt <= 8) LB_TILE(8, 8);
+    if (vt <= 12) LB_TILE(8, 12);
+    LB_TILE(8, 16);
+#undef LB_TILE
 }

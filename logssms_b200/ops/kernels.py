@@ -1596,3 +1596,43 @@ def pooled_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
              v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _code(q),
              _stream()), "pooled_attention", f"(dim {dim}, value dim {vdim})")
     return out
+
+
+POOLED_TILE = os.environ.get("LOGSSMS_B200_POOLED_TILE", "1") != "0"
+_pooled_tile_q = None
+
+
+def pooled_attention_tile_q() -> int:
+    """Query tokens per CTA of the tensor-core form (the kernel's constant)."""
+    global _pooled_tile_q
+    if _pooled_tile_q is None:
+        _pooled_tile_q = int(_fn("attention_pooled", "lb_pooled_attention_tile_q", [])())
+    return _pooled_tile_q
+
+
+def pooled_attention_tile_ok(q: torch.Tensor, v_cache: torch.Tensor) -> bool:
+    """Does the tensor-core form take these sizes?  bfloat16, a head size that is a multiple of 16 and a value head size
+    that is a multiple of 8, both up to 128."""
+    dim, vdim = q.shape[2], v_cache.shape[3]
+    return POOLED_TILE and q.dtype == torch.bfloat16 and dim % 16 == 0 and dim <= 128 and vdim % 8 == 0 and vdim <= 128
+
+
+def pooled_attention_tile(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
+                          block_table: torch.Tensor, pooled_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
+                          tiles: torch.Tensor, v_table: torch.Tensor, scale: float, window: int, pool: int, out: torch.Tensor) -> torch.Tensor:
+    """The same attention for the long portions' runs of `pooled_attention_tile_q()` tokens (work list of
+    `StepContext.long_portion_tiles`) on the tensor cores; writes those tokens' rows of `out` [tokens, heads * value_dim]."""
+    _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, cu_seqlens, start_pos, tiles, v_table, out)
+    for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (tiles, "tiles")):
+        _i32(t, name)
+    T, H, dim = q.shape
+    G, vdim = v_cache.shape[2], v_cache.shape[3]
+    _need(q.is_contiguous() and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and out.is_contiguous() and out.shape == (T, H * vdim), "the tensor-core form takes contiguous bfloat16 tensors")
+    f = _fn("attention_pooled", "lb_pooled_attention_tile", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                             c_void_p, c_int, c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(pooled_table), pooled_table.shape[1], _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(v_table),
+             v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _stream()),
+           "pooled_attention_tile", f"(dim {dim}, value dim {vdim})")
+    return out

@@ -33,7 +33,9 @@ class PooledWindowAttention(Part):
 
     Two paged needs: the tokens' keys and values in a group with a window (pages go back once the window and the
     block that is being filled have passed them), and the blocks' means in a group of one entry per `pool` tokens that
-    is kept for the request's life.  The token that ends a block writes the block's means.  Tensors: q, k, v, o."""
+    is kept for the request's life.  The token that ends a block writes the block's means.  Prompt portions of a bfloat16
+    engine run on the tensor cores (`K.pooled_attention_tile`), everything else a warp per (token, head)
+    (`K.pooled_attention`).  Tensors: q, k, v, o."""
     kernels = ("attention_pooled", "rope", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
@@ -82,6 +84,19 @@ class PooledWindowAttention(Part):
         if writes_cache:
             K.pooled_blocks(k_cache, v_cache, kp_cache, vp_cache, ctx.positions, ctx.token_req, ctx.block_tables[gi],
                             ctx.slot_mappings[gp], s.pool)
-        o = K.pooled_attention(q, k_cache, v_cache, kp_cache, vp_cache, ctx.block_tables[gi], ctx.block_tables[gp], ctx.token_req,
-                               ctx.positions, self.value_position.table, s.softmax_scale, s.window, s.pool)
+        tables = (ctx.block_tables[gi], ctx.block_tables[gp])
+        if ctx.has_long_portions and K.pooled_attention_tile_ok(q, v_cache):
+            # long portions on the tensor cores: runs of neighbouring tokens share their keys through shared memory; decoded
+            # tokens and short portions (other rows of the output) a warp per (token, head)
+            tiles, _ = ctx.long_portion_tiles(K.pooled_attention_tile_q())
+            short, n_short = ctx.short_portion_tokens()
+            o = torch.empty((x.shape[0], s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
+            K.pooled_attention_tile(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.cu_seqlens, ctx.start_pos, tiles,
+                                    self.value_position.table, s.softmax_scale, s.window, s.pool, o)
+            if n_short > 0:
+                K.pooled_attention(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.token_req, ctx.positions,
+                                   self.value_position.table, s.softmax_scale, s.window, s.pool, token_list=short, out=o)
+        else:
+            o = K.pooled_attention(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.token_req, ctx.positions,
+                                   self.value_position.table, s.softmax_scale, s.window, s.pool)
         return K.linear(o, self.o_w)

@@ -45,12 +45,13 @@ def turn_pairs(x, pos, base, dims):
     """Rotate the first `dims` columns of every row of x [..., n]: column 2i with column 2i + 1 by the angle
     pos * base^(-2i / dims).  `pos` may be negative (turning back)."""
     out = x.clone()
-    for i in range(dims // 2):
-        a = pos * base ** (-2.0 * i / dims)
-        c, s = math.cos(a), math.sin(a)
-        u, v = x[..., 2 * i], x[..., 2 * i + 1]
-        out[..., 2 * i] = u * c - v * s
-        out[..., 2 * i + 1] = v * c + u * s
+    if dims == 0:
+        return out
+    a = pos * torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)
+    c, s = torch.cos(a).to(x.dtype), torch.sin(a).to(x.dtype)
+    u, v = x[..., 0:dims:2], x[..., 1:dims:2]
+    out[..., 0:dims:2] = u * c - v * s
+    out[..., 1:dims:2] = v * c + u * s
     return out
 
 
@@ -101,13 +102,13 @@ def pooled_window_attention(h, W, state, *, heads, kv_heads, dim, vdim, scale, w
         i = start + t
         first = max(0, i - window + 1)                       # the oldest token inside the window
         blocks = max(0, (i - window + 1) // pool)             # blocks that lie wholly behind the window
+        # what position i sees: one mean per block, then the window's tokens  [n, kv_heads, .]
+        keys = torch.cat([k[:blocks * pool].reshape(blocks, pool, kv_heads, dim).mean(1), k[first:i + 1]])
+        vals = torch.cat([v[:blocks * pool].reshape(blocks, pool, kv_heads, vdim).mean(1), v[first:i + 1]])
         for hd in range(heads):
             g = hd // per
-            keys = [k[b * pool:(b + 1) * pool, g].mean(0) for b in range(blocks)] + [k[j, g] for j in range(first, i + 1)]
-            vals = [v[b * pool:(b + 1) * pool, g].mean(0) for b in range(blocks)] + [v[j, g] for j in range(first, i + 1)]
-            s = torch.stack(keys) @ q[t, hd] * scale
-            p = torch.softmax(s, 0)
-            out[t, hd] = turn_pairs(p @ torch.stack(vals), -i, base, vdim)
+            p = torch.softmax(keys[:, g] @ q[t, hd] * scale, 0)
+            out[t, hd] = turn_pairs(p @ vals[:, g], -i, base, vdim)
     return out.reshape(T, heads * vdim) @ W["o"].T
 
 
@@ -118,9 +119,14 @@ def dense_ff(h, W, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W["down"].T
 
 
-def moe_ff(h, W, *, experts, top):
+def moe_ff(h, W, *, experts, top, margins=None):
+    """`margins` (a list): per token the gap between the last chosen score and the best one left out is appended (a
+    small gap is a choice that rounding may turn)."""
     s = torch.sigmoid(h @ W["router"].T)                      # [T, experts]
     out = torch.zeros_like(h)
+    if margins is not None:
+        ranked = s.sort(-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if experts > top else torch.ones_like(s[:, 0]))
     for t in range(h.shape[0]):
         for e in torch.topk(s[t], top).indices.tolist():
             x = s[t, e] * h[t]
@@ -156,8 +162,9 @@ class PlainKuvazen:
     def new_state(self):
         return {"runs": [dict() for _ in self.runs]}
 
-    def forward(self, ids, state, layer_outputs=None):
-        """Logits [T, vocab] of the next `ids` of a sequence whose earlier tokens left `state`."""
+    def forward(self, ids, state, layer_outputs=None, margins=None):
+        """Logits [T, vocab] of the next `ids` of a sequence whose earlier tokens left `state`.  `margins` (a list) gets
+        one tensor [T] per routed layer run: how clear the router's choice was (see `moe_ff`)."""
         cfg, eps = self.cfg, self.cfg["norm"]["eps"]
         ids = list(ids)
         x = layer_norm(self.w["embed"][torch.as_tensor(ids)], self.w["embed.norm"], eps)
@@ -182,9 +189,10 @@ class PlainKuvazen:
                 if ff["kind"] == "dense":
                     y = dense_ff(hin, W, ff["limit"])
                 else:
-                    y = moe_ff(hin, W, experts=ff["router"]["experts"], top=ff["router"]["top"])
+                    y = moe_ff(hin, W, experts=ff["router"]["experts"], top=ff["router"]["top"], margins=margins)
                 x = x + self.w[f"l{i}.ls2"] * y
-            x = side_input(x, ids, i, self.w["side.embed"], self._sub(f"l{i}.side."), cfg["token_side"]["dim"], eps)
+            if cfg.get("token_side"):
+                x = side_input(x, ids, i, self.w["side.embed"], self._sub(f"l{i}.side."), cfg["token_side"]["dim"], eps)
             if layer_outputs is not None:
                 layer_outputs.append(x)
         return layer_norm(x, self.w["final.norm"], eps) @ self.w["head"].T
