@@ -15,7 +15,9 @@
 //   pooled_blocks  : per token that ends a block: the means of the block's cached keys and values, stored at the
 //                    block's entry of a second paged cache (one entry per `pool` tokens)
 //   pooled_attention      : a warp per (token, head); a lane scores one key at a time, the lanes share the value
-//                           columns; scores, softmax and sums in float32 (every dtype, every size, every step)
+//                           columns; scores, softmax and sums in float32 (every dtype, every size)
+//   pooled_attention_split: decoded tokens and short portions: key ranges side by side, all query heads of a key/value
+//                           head in one CTA, a merge kernel behind (described at the kernel)
 //   pooled_attention_tile : bfloat16 prompt portions on the tensor cores: a CTA per (run of up to 64 neighbouring tokens
 //                           of a request, query head); the keys the run sees go through shared memory once for all
 //                           its queries (described at the kernel)
@@ -236,6 +238,232 @@ extern "C" int lb_pooled_attention(const void* q, const void* k_cache, const voi
         (const T*)q, (const T*)k_cache, (const T*)v_cache, (const T*)kp_cache, (const T*)vp_cache, block_table, table_width,
         pooled_table, pooled_width, token_req, positions, token_list, v_table, v_rot, table_rows, (T*)out, Hq, Hkv, dim, vdim,
         page_size, scale, window, pool));
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------ decoded tokens: key ranges side by side
+// A CTA takes one token, one key/value head and one of `splits` ranges of the token's keys (pooled blocks first, then
+// the window's tokens) for ALL query heads of that key/value head: a lane scores one key at a time for every head
+// (the key row is read once, in 16-byte pieces where the size allows), then the lanes share the value columns of
+// the warp's 32 keys.  The four warps' partial (maximum, sum, weighted values) meet in shared memory and go to a
+// scratch buffer; `pooled_merge` joins the ranges, divides, turns the values back and stores.  All float32.
+constexpr int kSplitWarps = 4;
+constexpr int kSplitValueRegs = 4;        // value columns per lane: vdim <= 128
+
+template <typename T, int kPer>
+__device__ __forceinline__ void score_row(const T* __restrict__ kr, const float* __restrict__ qs, int dim, float (&s)[kPer]) {
+    for (int c = 0; c < dim; ++c) {
+        const float kv = to_f32(kr[c]);
+#pragma unroll
+        for (int h = 0; h < kPer; ++h) s[h] += qs[h * dim + c] * kv;
+    }
+}
+template <int kPer>
+__device__ __forceinline__ void score_row_vec(const __nv_bfloat16* __restrict__ kr, const float* __restrict__ qs, int dim, float (&s)[kPer]) {
+    for (int c = 0; c < dim; c += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float kv[8];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) { const float2 f = __bfloat1622float2(p2[x]); kv[2 * x] = f.x; kv[2 * x + 1] = f.y; }
+#pragma unroll
+        for (int h = 0; h < kPer; ++h) {
+            const float4 q0 = *reinterpret_cast<const float4*>(qs + h * dim + c), q1 = *reinterpret_cast<const float4*>(qs + h * dim + c + 4);
+            s[h] += q0.x * kv[0] + q0.y * kv[1] + q0.z * kv[2] + q0.w * kv[3] + q1.x * kv[4] + q1.y * kv[5] + q1.z * kv[6] + q1.w * kv[7];
+        }
+    }
+}
+
+// grid (tokens, Hkv * ceil(per / kPer), splits); dynamic shared memory: kPer * dim floats (queries) + the warps' partial results
+// partial: float [tokens, Hq, splits, vdim + 2] (maximum, sum, weighted values)
+template <typename T, int kPer>
+__global__ void __launch_bounds__(kSplitWarps * 32) pooled_attention_split_kernel(
+        const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, const T* __restrict__ kp_cache,
+        const T* __restrict__ vp_cache, const int* __restrict__ block_table, int table_width, const int* __restrict__ pooled_table,
+        int pooled_width, const int* __restrict__ token_req, const int* __restrict__ positions, const int* __restrict__ token_list,
+        float* __restrict__ partial, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, int splits) {
+    extern __shared__ __align__(16) float split_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slot = blockIdx.x;                                   // row of the scratch buffer
+    const int t = token_list != nullptr ? token_list[slot] : slot;
+    if (t < 0) return;
+    const int per = Hq / Hkv, groups = (per + kPer - 1) / kPer;
+    const int g = blockIdx.y / groups, h0 = g * per + (blockIdx.y % groups) * kPer;
+    const int nh = min(kPer, g * per + per - h0);                  // query heads of this CTA
+    const int split = blockIdx.z;
+    float* qs = split_smem;                                        // [kPer][dim]
+    float* part = split_smem + kPer * dim;                         // [warps][kPer][vdim + 2]
+    for (int i = threadIdx.x; i < kPer * dim; i += blockDim.x) {
+        const int h = i / dim, c = i % dim;
+        qs[i] = h < nh ? to_f32(q[((size_t)t * Hq + h0 + h) * dim + c]) * scale : 0.f;
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    const int* pages = block_table + (size_t)token_req[t] * table_width;
+    const int* pooled_pages = pooled_table + (size_t)token_req[t] * pooled_width;
+    const int first = max(0, pos - window + 1);
+    const int blocks = max(0, (pos - window + 1) / pool);
+    const int keys = blocks + (pos - first + 1);
+    const int chunk = ((keys + splits - 1) / splits + 31) / 32 * 32;
+    const int k_begin = split * chunk, k_end = min(keys, k_begin + chunk);
+    const bool vec = sizeof(T) == 2 && dim % 8 == 0;
+    float m[kPer], l[kPer], acc[kPer][kSplitValueRegs];
+#pragma unroll
+    for (int h = 0; h < kPer; ++h) {
+        m[h] = -INFINITY; l[h] = 0.f;
+#pragma unroll
+        for (int r = 0; r < kSplitValueRegs; ++r) acc[h][r] = 0.f;
+    }
+    for (int k0 = k_begin + warp * 32; k0 < k_end; k0 += kSplitWarps * 32) {
+        const int kk = k0 + lane;
+        float s[kPer];
+#pragma unroll
+        for (int h = 0; h < kPer; ++h) s[h] = 0.f;
+        long row = -1;
+        bool pooled = false;
+        if (kk < k_end) row = key_row(kk, blocks, first, pages, pooled_pages, page_size, pooled);
+        if (row >= 0) {
+            const T* kr = (pooled ? kp_cache : k_cache) + ((size_t)row * Hkv + g) * dim;
+            if (vec) score_row_vec<kPer>(reinterpret_cast<const __nv_bfloat16*>(kr), qs, dim, s);
+            else score_row<T, kPer>(kr, qs, dim, s);
+        }
+        float p[kPer];
+#pragma unroll
+        for (int h = 0; h < kPer; ++h) {
+            const float sv = row >= 0 ? s[h] : -INFINITY;
+            const float m_new = fmaxf(m[h], warp_max(sv));
+            const float corr = (m[h] == -INFINITY) ? 0.f : expf(m[h] - m_new);
+            p[h] = (sv == -INFINITY) ? 0.f : expf(sv - m_new);
+            l[h] = l[h] * corr + warp_sum(p[h]);
+            m[h] = m_new;
+#pragma unroll
+            for (int r = 0; r < kSplitValueRegs; ++r) acc[h][r] *= corr;
+        }
+        const int n = min(32, k_end - k0);
+        for (int j = 0; j < n; ++j) {
+            const long rj = __shfl_sync(0xffffffffu, row, j);
+            if (rj < 0) continue;
+            const T* vr = ((k0 + j) < blocks ? vp_cache : v_cache) + ((size_t)rj * Hkv + g) * vdim;
+            float vv[kSplitValueRegs];
+#pragma unroll
+            for (int r = 0; r < kSplitValueRegs; ++r) { const int c = lane + 32 * r; vv[r] = c < vdim ? to_f32(vr[c]) : 0.f; }
+#pragma unroll
+            for (int h = 0; h < kPer; ++h) {
+                const float pj = __shfl_sync(0xffffffffu, p[h], j);
+#pragma unroll
+                for (int r = 0; r < kSplitValueRegs; ++r) acc[h][r] += pj * vv[r];
+            }
+        }
+    }
+    // the warps' partial results meet: warp 0 joins them
+    const int stride = vdim + 2;
+#pragma unroll
+    for (int h = 0; h < kPer; ++h) {
+        float* dst = part + ((size_t)warp * kPer + h) * stride;
+        if (lane == 0) { dst[0] = m[h]; dst[1] = l[h]; }
+#pragma unroll
+        for (int r = 0; r < kSplitValueRegs; ++r) { const int c = lane + 32 * r; if (c < vdim) dst[2 + c] = acc[h][r]; }
+    }
+    __syncthreads();
+    for (int h = warp; h < nh; h += kSplitWarps) {
+        float mm = -INFINITY;
+        for (int w = 0; w < kSplitWarps; ++w) mm = fmaxf(mm, part[((size_t)w * kPer + h) * stride]);
+        float ll = 0.f, o[kSplitValueRegs];
+#pragma unroll
+        for (int r = 0; r < kSplitValueRegs; ++r) o[r] = 0.f;
+        for (int w = 0; w < kSplitWarps; ++w) {
+            const float* src = part + ((size_t)w * kPer + h) * stride;
+            const float f = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mm);
+            ll += f * src[1];
+#pragma unroll
+            for (int r = 0; r < kSplitValueRegs; ++r) { const int c = lane + 32 * r; if (c < vdim) o[r] += f * src[2 + c]; }
+        }
+        float* dst = partial + (((size_t)slot * Hq + h0 + h) * splits + split) * stride;
+        if (lane == 0) { dst[0] = mm; dst[1] = ll; }
+#pragma unroll
+        for (int r = 0; r < kSplitValueRegs; ++r) { const int c = lane + 32 * r; if (c < vdim) dst[2 + c] = o[r]; }
+    }
+}
+
+// grid (tokens, Hq), a warp: joins the ranges, divides by the sum, turns the values back by the query's position
+template <typename T>
+__global__ void __launch_bounds__(32) pooled_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions,
+                                                          const int* __restrict__ token_list, const float* __restrict__ v_table, int v_rot,
+                                                          int table_rows, T* __restrict__ out, int Hq, int vdim, int splits) {
+    const int lane = threadIdx.x, slot = blockIdx.x, head = blockIdx.y;
+    const int t = token_list != nullptr ? token_list[slot] : slot;
+    if (t < 0) return;
+    const int stride = vdim + 2;
+    const float* src0 = partial + ((size_t)slot * Hq + head) * splits * stride;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, src0[(size_t)s * stride]);
+    float ll = 0.f, o[kSplitValueRegs];
+#pragma unroll
+    for (int r = 0; r < kSplitValueRegs; ++r) o[r] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* src = src0 + (size_t)s * stride;
+        const float f = (src[0] == -INFINITY) ? 0.f : expf(src[0] - mm);
+        ll += f * src[1];
+#pragma unroll
+        for (int r = 0; r < kSplitValueRegs; ++r) { const int c = lane + 32 * r; if (c < vdim) o[r] += f * src[2 + c]; }
+    }
+    const float inv_l = ll > 0.f ? 1.f / ll : 0.f;
+    const float* cs = v_table + (size_t)min(max(positions[t], 0), table_rows - 1) * v_rot;
+    const int half = v_rot >> 1;
+#pragma unroll
+    for (int r = 0; r < kSplitValueRegs; ++r) {
+        const int c = lane + 32 * r;
+        const float own = o[r] * inv_l;
+        const float partner = __shfl_xor_sync(0xffffffffu, own, 1);
+        if (c < vdim) {
+            float val = own;
+            if (c < v_rot) {
+                const float co = cs[c >> 1], si = cs[half + (c >> 1)];
+                val = (c & 1) ? own * co - partner * si : own * co + partner * si;
+            }
+            out[((size_t)t * Hq + head) * vdim + c] = from_f32<T>(val);
+        }
+    }
+}
+
+template <typename T, int kPer>
+static int launch_split(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache, const void* vp_cache,
+                        const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* token_req,
+                        const int* positions, const int* token_list, int num_tokens, float* partial, int Hq, int Hkv, int dim, int vdim,
+                        int page_size, float scale, int window, int pool, int splits, void* stream) {
+    const size_t smem = ((size_t)kPer * dim + (size_t)kSplitWarps * kPer * (vdim + 2)) * sizeof(float);
+    static size_t have = 0;
+    ensure_dynamic_smem(pooled_attention_split_kernel<T, kPer>, smem, have);
+    const int per = Hq / Hkv;
+    dim3 grid(num_tokens, Hkv * ((per + kPer - 1) / kPer), splits);
+    pooled_attention_split_kernel<T, kPer><<<grid, kSplitWarps * 32, smem, (cudaStream_t)stream>>>(
+        (const T*)q, (const T*)k_cache, (const T*)v_cache, (const T*)kp_cache, (const T*)vp_cache, block_table, table_width,
+        pooled_table, pooled_width, token_req, positions, token_list, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits);
+    return launch_status();
+}
+
+// partial: float32 scratch of num_tokens * Hq * splits * (vdim + 2); vdim <= 128; dim a multiple of 4
+extern "C" int lb_pooled_attention_split(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache,
+                                         const void* vp_cache, const int* block_table, int table_width, const int* pooled_table,
+                                         int pooled_width, const int* token_req, const int* positions, const int* token_list,
+                                         int num_tokens, const float* v_table, int v_rot, int table_rows, float* partial, void* out,
+                                         int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
+                                         int splits, int dtype, void* stream) {
+    if (num_tokens <= 0) return kOk;
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || dim <= 0 || dim % 4 || vdim <= 0 || page_size <= 0 || window <= 0 || pool <= 0 || (v_rot & 1)
+        || v_rot > vdim || table_rows <= 0 || splits <= 0 || splits > 65535 || Hq > 65535)
+        return kBadSize;
+    if (vdim > 32 * kSplitValueRegs || dim > 1024) return kTooLarge;
+    const int per = Hq / Hkv;
+    int code;
+#define LB_SPLIT(PER) LB_DISPATCH_DTYPE(dtype, code = (launch_split<T, PER>(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, \
+        pooled_table, pooled_width, token_req, positions, token_list, num_tokens, partial, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits, stream)))
+    if (per == 1) { LB_SPLIT(1); } else if (per == 2) { LB_SPLIT(2); } else { LB_SPLIT(4); }
+#undef LB_SPLIT
+    if (code != 0) return code;
+    dim3 grid(num_tokens, Hq);
+    LB_DISPATCH_DTYPE(dtype, pooled_merge_kernel<T><<<grid, 32, 0, (cudaStream_t)stream>>>(partial, positions, token_list, v_table, v_rot,
+                                                                                           table_rows, (T*)out, Hq, vdim, splits));
     return launch_status();
 }
 

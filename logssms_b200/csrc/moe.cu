@@ -62,9 +62,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     }
     __syncwarp();
     for (int e = lane; e < n; e += 32) {
-        const float s = sigmoid_scores ? 1.f / (1.f + expf(-z[e])) : expf(z[e] - mx) / sum;
+        const float logit = z[e];
+        const float s = sigmoid_scores ? 1.f / (1.f + expf(-logit)) : expf(logit - mx) / sum;
         z[e] = s;
-        c[e] = s + (correction != nullptr ? correction[e] : 0.f);
+        // sigmoid scores without a correction are ranked by their logits: the same order, and two large logits do not
+        // meet in a score that has rounded to 1
+        c[e] = (sigmoid_scores && correction == nullptr) ? logit : s + (correction != nullptr ? correction[e] : 0.f);
         ok[e] = 0;
         dense[(size_t)t * n + e] = 0.f;
     }

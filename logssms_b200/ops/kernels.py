@@ -1409,7 +1409,7 @@ def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- pre-norm layers on a 32-bit stream
-NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1, "none": 2}
 
 
 def embed_norm(table: torch.Tensor, ids: torch.Tensor, weight: torch.Tensor, eps: float, kind: str,
@@ -1429,47 +1429,63 @@ def embed_norm(table: torch.Tensor, ids: torch.Tensor, weight: torch.Tensor, eps
 
 
 def stream_add_norm(x: torch.Tensor, y: torch.Tensor | None, channel_scale: torch.Tensor | None, weight: torch.Tensor | None,
-                    eps: float, kind: str, act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:
-    """x += channel_scale * y in place (x: the float32 stream; y: activations or None), then norm(x) * weight rounded to
-    `act_dtype` (None without a weight).  Returns (x, normed)."""
+                    eps: float, kind: str, act_dtype: torch.dtype, unit_eps: float | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """x += channel_scale * y in place (x: the float32 stream; y: activations or None; with `unit_eps` y is first divided
+    by sqrt(mean(y^2) + unit_eps)), then norm(x) * weight rounded to `act_dtype` (None without a weight; kind "none": x
+    rounded).  Returns (x, normed)."""
     _cuda(x, y, channel_scale, weight)
     rows, H = x.shape
     _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
     _need(y is None or (y.shape == x.shape and y.dtype == act_dtype and y.is_contiguous()), "y must match the stream's shape")
     for v, name in ((channel_scale, "channel_scale"), (weight, "weight")):
         _need(v is None or (v.dtype == torch.float32 and v.shape == (H,) and v.is_contiguous()), f"{name} must be float32 [width]")
-    _need(y is not None or weight is not None, "nothing to do")
-    h = None if weight is None else torch.empty((rows, H), dtype=act_dtype, device=x.device)
-    f = _fn("stream_layer", "lb_stream_add_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(y), _ptr(channel_scale), _ptr(weight), eps, _ptr(x) if y is not None else None, _ptr(h), rows, H,
-             NORM_KINDS[kind], _DTYPE_CODE[act_dtype], _stream()), "stream_add_norm", f"(width {H})")
+    _need(y is not None or weight is not None or kind == "none", "nothing to do")
+    h = None if (weight is None and kind != "none") else torch.empty((rows, H), dtype=act_dtype, device=x.device)
+    f = _fn("stream_layer", "lb_stream_add_norm", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                                   c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(y), _ptr(channel_scale), -1.0 if unit_eps is None else unit_eps, _ptr(weight), eps,
+             _ptr(x) if y is not None else None, _ptr(h), rows, H, NORM_KINDS[kind], _DTYPE_CODE[act_dtype], _stream()),
+           "stream_add_norm", f"(width {H})")
     return x, h
 
 
+def side_gate(z: torch.Tensor, ids: torch.Tensor, side_table: torch.Tensor, offset: int) -> torch.Tensor:
+    """gelu_tanh(z) * e for z [tokens, dim], e the columns [offset, offset + dim) of side_table[id]."""
+    _cuda(z, ids, side_table)
+    _i32(ids, "ids")
+    _need(z.dim() == 2 and z.is_contiguous() and side_table.dim() == 2 and side_table.is_contiguous() and side_table.dtype == z.dtype,
+          "side_gate wants contiguous z [tokens, dim] and a table of its dtype")
+    a = torch.empty_like(z)
+    f = _fn("stream_layer", "lb_side_gate", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(z), _ptr(ids), _ptr(side_table), side_table.shape[1], offset, side_table.shape[0], _ptr(a), z.shape[0], z.shape[1],
+             _code(z), _stream()), "side_gate")
+    return a
+
+
 def stream_side(x: torch.Tensor, y: torch.Tensor | None, channel_scale: torch.Tensor | None, ids: torch.Tensor,
-                side_table: torch.Tensor, offset: int, gate_w: torch.Tensor, proj_w: torch.Tensor, side_w: torch.Tensor,
+                side_table: torch.Tensor, offset: int, gate_w: torch.Tensor, proj_t: torch.Tensor, side_w: torch.Tensor,
                 side_eps: float, next_weight: torch.Tensor | None, next_eps: float, next_kind: str,
                 act_dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor | None]:
-    """x += channel_scale * y, then the token's side input x += RMSNorm(proj_w (gelu_tanh(gate_w x) * e)) * side_w with e the
+    """x += channel_scale * y, then the token's side input x += RMSNorm(proj (gelu_tanh(gate_w x) * e)) * side_w with e the
     columns [offset, offset + dim) of side_table[id], all in place on the float32 stream; with `next_weight` also the
-    norm that reads the stream next, rounded to `act_dtype`.  Returns (x, normed or None)."""
-    _cuda(x, y, channel_scale, ids, side_table, gate_w, proj_w, side_w, next_weight)
+    norm that reads the stream next, rounded to `act_dtype`.  `proj_t` is the projection transposed, [dim, width].
+    Returns (x, normed or None)."""
+    _cuda(x, y, channel_scale, ids, side_table, gate_w, proj_t, side_w, next_weight)
     _i32(ids, "ids")
     rows, H = x.shape
     dim = gate_w.shape[0]
     _need(x.dtype == torch.float32 and x.is_contiguous(), "the stream must be contiguous float32")
     _need(y is None or (y.shape == x.shape and y.dtype == act_dtype and y.is_contiguous()), "y must match the stream's shape")
-    _need(gate_w.shape == (dim, H) and proj_w.shape == (H, dim) and gate_w.is_contiguous() and proj_w.is_contiguous()
-          and gate_w.dtype == proj_w.dtype == side_table.dtype == act_dtype and side_table.dim() == 2 and side_table.is_contiguous(),
-          "side input wants gate [dim, width], proj [width, dim] and a [vocab, columns] table in the activation dtype")
+    _need(gate_w.shape == (dim, H) and proj_t.shape == (dim, H) and gate_w.is_contiguous() and proj_t.is_contiguous()
+          and gate_w.dtype == proj_t.dtype == side_table.dtype == act_dtype and side_table.dim() == 2 and side_table.is_contiguous(),
+          "side input wants gate [dim, width], the projection transposed [dim, width] and a [vocab, columns] table in the activation dtype")
     for v, name in ((channel_scale, "channel_scale"), (side_w, "side norm weight"), (next_weight, "next norm weight")):
         _need(v is None or (v.dtype == torch.float32 and v.shape == (H,) and v.is_contiguous()), f"{name} must be float32 [width]")
     h = None if next_weight is None else torch.empty((rows, H), dtype=act_dtype, device=x.device)
     f = _fn("stream_layer", "lb_stream_side", [c_void_p] * 5 + [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                                c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(y), _ptr(channel_scale), _ptr(ids), _ptr(side_table), side_table.shape[1], offset, side_table.shape[0],
-             _ptr(gate_w), _ptr(proj_w), _ptr(side_w), side_eps, dim, _ptr(next_weight), next_eps, NORM_KINDS[next_kind], _ptr(x),
+             _ptr(gate_w), _ptr(proj_t), _ptr(side_w), side_eps, dim, _ptr(next_weight), next_eps, NORM_KINDS[next_kind], _ptr(x),
              _ptr(h), rows, H, _DTYPE_CODE[act_dtype], _stream()), "stream_side", f"(width {H}, side {dim})")
     return x, h
 
@@ -1635,4 +1651,40 @@ def pooled_attention_tile(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
              _ptr(pooled_table), pooled_table.shape[1], _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(v_table),
              v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _stream()),
            "pooled_attention_tile", f"(dim {dim}, value dim {vdim})")
+    return out
+
+
+def pooled_attention_split_ok(q: torch.Tensor, v_cache: torch.Tensor) -> bool:
+    """Does the form with key ranges take these sizes?  A value head size up to 128, a head size that is a multiple of 4."""
+    return q.shape[2] % 4 == 0 and q.shape[2] <= 1024 and v_cache.shape[3] <= 128
+
+
+def pooled_splits(num_tokens: int, num_kv_heads: int, keys: int) -> int:
+    """Key ranges per token so that the CTAs fill the GPU about twice (each takes at least 128 keys)."""
+    return max(1, min(-(-keys // 128), -(-2 * _SM_COUNT // max(num_tokens * num_kv_heads, 1)), 64))
+
+
+def pooled_attention_split(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
+                           block_table: torch.Tensor, pooled_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                           v_table: torch.Tensor, scale: float, window: int, pool: int, splits: int,
+                           token_list: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The attention of `pooled_attention` with every token's keys cut into `splits` ranges that run side by side and all
+    query heads of a key/value head in one CTA; a merge kernel joins the ranges (two launches)."""
+    _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, token_req, positions, v_table, token_list)
+    for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, name)
+    T, H, dim = q.shape
+    G, vdim = v_cache.shape[2], v_cache.shape[3]
+    _need(q.is_contiguous() and q.dtype == k_cache.dtype, "queries must be contiguous [tokens, heads, dim] in the cache's dtype")
+    if out is None:
+        out = torch.empty((T, H * vdim), dtype=q.dtype, device=q.device)
+    n = T if token_list is None else token_list.numel()
+    partial = torch.empty((n, H, splits, vdim + 2), dtype=torch.float32, device=q.device)
+    f = _fn("attention_pooled", "lb_pooled_attention_split", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                              c_void_p, c_int, c_int, c_void_p, c_void_p] + [c_int] * 5
+            + [c_float, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
+             _ptr(pooled_table), pooled_table.shape[1], _ptr(token_req), _ptr(positions), _ptr(token_list), n, _ptr(v_table),
+             v_table.shape[1], max(v_table.shape[0], 1), _ptr(partial), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
+             splits, _code(q), _stream()), "pooled_attention_split", f"(dim {dim}, value dim {vdim}, {splits} ranges)", launches=2)
     return out

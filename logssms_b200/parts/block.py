@@ -220,9 +220,11 @@ class SharedTable(Part):
 class TokenSideInput(Part):
     """A layer's input from the token itself: x <- x + RMSNorm(proj (gelu_tanh(gate x) * e)) * norm, where e are this
     layer's `dim` columns of the token's row of a side table that all layers share (one tensor at the model's root).
-    It runs inside the kernel that closes the layer (`K.stream_side`).  Tensors: gate [dim, width], proj [width, dim],
+    It runs inside the kernel that closes the layer (`K.stream_side`); in steps of many tokens of a bfloat16 engine the two
+    small products go to the library between three light kernels.  Tensors: gate [dim, width], proj [width, dim],
     norm [width]; the table under `spec.table_name`."""
-    kernels = ("stream_layer",)
+    kernels = ("stream_layer", "linear_skinny", "gemm_tcgen05")
+    FUSED_MAX_ROWS = 128      # up to so many tokens one kernel does it all; beyond, the products go to the library
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
         from .base import MATRIX, VECTOR, ParamSpec, normal_init, ones_init
@@ -239,19 +241,24 @@ class TokenSideInput(Part):
         elif not isinstance(table, SharedTable) or table.name != name or table.shape != (spec.vocab_size, spec.table_width):
             raise ValueError(f"the layers disagree on the side table {spec.table_name!r}")
         self.shared_table = table
-        self.gate = self.proj = self.norm = None
+        self.gate = self.proj = self.proj_t = self.norm = None
 
     def param_specs(self):
         return dict(self._specs)
 
     def bind(self, t):
-        self.gate, self.proj, self.norm = t["gate"], t["proj"], t["norm"]
+        self.gate, self.proj, self.proj_t, self.norm = t["gate"], t["proj"], t["proj"].t().contiguous(), t["norm"]
 
     def close(self, x_f32, y, channel_scale, ids, next_norm, act_dtype):
         """x += channel_scale * y (y may be None), the side input, and the norm that follows; (x, normed or None)."""
         s = self.spec
         nw, neps, nkind = (None, 0.0, "layernorm") if next_norm is None else (next_norm.weight, next_norm.eps, next_norm.norm_kind)
-        return K.stream_side(x_f32, y, channel_scale, ids, self.shared_table.table, s.offset, self.gate, self.proj, self.norm,
+        if x_f32.shape[0] > self.FUSED_MAX_ROWS and act_dtype == torch.bfloat16:
+            # many tokens: the two small products on the tensor cores (the library), three light kernels around them
+            _, rounded = K.stream_add_norm(x_f32, y, channel_scale, None, 0.0, "none", act_dtype)
+            a = K.side_gate(K.linear(rounded, self.gate), ids, self.shared_table.table, s.offset)
+            return K.stream_add_norm(x_f32, K.linear(a, self.proj), self.norm, nw, neps, nkind, act_dtype, unit_eps=s.eps)
+        return K.stream_side(x_f32, y, channel_scale, ids, self.shared_table.table, s.offset, self.gate, self.proj_t, self.norm,
                              s.eps, nw, neps, nkind, act_dtype)
 
 
@@ -329,7 +336,7 @@ class PreNormStreamBlock(Part):
             _, h = K.stream_add_norm(stream, None, None, self.mixer_norm.weight, self.mixer_norm.eps, self.mixer_norm.norm_kind, act)
         with nvtx_range(self.spec.mixer.spec.kind):
             y = self.mixer.forward(h, ctx, cache_layer, writes_cache)
-        scale, y_scale = self.scale_mixer, None
+        scale = self.scale_mixer
         if self.feed_forward is not None:
             _, h = K.stream_add_norm(stream, y, scale, self.ff_norm.weight, self.ff_norm.eps, self.ff_norm.norm_kind, act)
             with nvtx_range(self.spec.feed_forward.kind):

@@ -34,8 +34,9 @@ class PooledWindowAttention(Part):
     Two paged needs: the tokens' keys and values in a group with a window (pages go back once the window and the
     block that is being filled have passed them), and the blocks' means in a group of one entry per `pool` tokens that
     is kept for the request's life.  The token that ends a block writes the block's means.  Prompt portions of a bfloat16
-    engine run on the tensor cores (`K.pooled_attention_tile`), everything else a warp per (token, head)
-    (`K.pooled_attention`).  Tensors: q, k, v, o."""
+    engine run on the tensor cores (`K.pooled_attention_tile`); decoded tokens, short portions and float32 engines cut
+    every token's keys into ranges that run side by side (`K.pooled_attention_split`), or, for sizes that form does not
+    take, run a warp per (token, head) (`K.pooled_attention`).  Tensors: q, k, v, o."""
     kernels = ("attention_pooled", "rope", "linear_skinny", "gemm_tcgen05")
 
     def __init__(self, spec, perturb_init: bool = False, shared: dict | None = None):
@@ -85,6 +86,18 @@ class PooledWindowAttention(Part):
             K.pooled_blocks(k_cache, v_cache, kp_cache, vp_cache, ctx.positions, ctx.token_req, ctx.block_tables[gi],
                             ctx.slot_mappings[gp], s.pool)
         tables = (ctx.block_tables[gi], ctx.block_tables[gp])
+        # the most keys a token of this step sees (a captured step is replayed for other positions: `max_context` is
+        # then the engine's limit)
+        most_keys = min(s.window, ctx.max_context) + ctx.max_context // s.pool
+
+        def few_rows(token_list=None, out=None, n=x.shape[0]):
+            # decoded tokens and short portions: key ranges side by side where the sizes allow, else a warp per (token, head)
+            args = (q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.token_req, ctx.positions, self.value_position.table,
+                    s.softmax_scale, s.window, s.pool)
+            if K.pooled_attention_split_ok(q, v_cache):
+                return K.pooled_attention_split(*args, K.pooled_splits(n, s.num_kv_heads, most_keys), token_list=token_list, out=out)
+            return K.pooled_attention(*args, token_list=token_list, out=out)
+
         if ctx.has_long_portions and K.pooled_attention_tile_ok(q, v_cache):
             # long portions on the tensor cores: runs of neighbouring tokens share their keys through shared memory; decoded
             # tokens and short portions (other rows of the output) a warp per (token, head)
@@ -94,9 +107,7 @@ class PooledWindowAttention(Part):
             K.pooled_attention_tile(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.cu_seqlens, ctx.start_pos, tiles,
                                     self.value_position.table, s.softmax_scale, s.window, s.pool, o)
             if n_short > 0:
-                K.pooled_attention(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.token_req, ctx.positions,
-                                   self.value_position.table, s.softmax_scale, s.window, s.pool, token_list=short, out=o)
+                few_rows(short, o, n_short)
         else:
-            o = K.pooled_attention(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.token_req, ctx.positions,
-                                   self.value_position.table, s.softmax_scale, s.window, s.pool)
+            o = few_rows()
         return K.linear(o, self.o_w)

@@ -75,10 +75,13 @@ def test_channel_scaled_sum_and_norm_of_a_stream(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [9, 300])          # few rows: one kernel; many (bfloat16): the two small products go to the library
 @pytest.mark.parametrize("width, dim, layer, layers", [(72, 6, 0, 3), (264, 1, 2, 3), (96, 24, 1, 2), (1030, 40, 3, 4)])
-def test_token_side_input_closes_a_layer(dtype, width, dim, layer, layers):
+def test_token_side_input_closes_a_layer(dtype, width, dim, layer, layers, rows):
     from logssms_b200.config.specs import NormSpec, TokenSideSpec
     from logssms_b200.parts import LayerNorm, TokenSideInput
+    if dim == 1 and rows > 9 and dtype == torch.bfloat16:
+        pytest.skip("one column: the side input is +- a fixed vector, by the sign of one product of rounded rows")
     shared = {}
     spec = TokenSideSpec(width, dim, layer * dim, layers * dim, 31, 1e-5)
     side = TokenSideInput(spec, perturb_init=True, shared=shared)
@@ -89,10 +92,10 @@ def test_token_side_input_closes_a_layer(dtype, width, dim, layer, layers):
     nxt = LayerNorm(NormSpec(width, 1e-6, kind="layernorm", param_name=""), perturb_init=True)
     nw = f64(give_weights(nxt, dtype, seed=4))[""]
     g = torch.Generator().manual_seed(2)
-    x = torch.randn(9, width, generator=g) * 2
-    y = torch.randn(9, width, generator=g).to(dtype)
+    x = torch.randn(rows, width, generator=g) * 2
+    y = torch.randn(rows, width, generator=g).to(dtype)
     ls = torch.rand(width, generator=g) + 0.5
-    ids = torch.randint(0, 31, (9,), generator=g)
+    ids = torch.randint(0, 31, (rows,), generator=g)
     joined = x.double() + ls.double() * y.double()
     want = P.side_input(joined, ids.tolist(), layer, tw, w, dim, 1e-5)
     assert float((want - joined).abs().max()) > 0.1              # the side input does move the stream
@@ -263,10 +266,11 @@ def test_the_output_names_every_token_and_block_that_was_seen(window, pool):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window, pool", [(6, 4), (16, 16), (17, 5), (1, 3), (5, 9), (48, 1), (33, 32), (64, 8), (70, 64)])
 def test_a_histogram_of_what_was_seen_on_the_tensor_cores_and_off(dtype, window, pool):
-    """Equal scores (zero queries) and values that are unit vectors by position modulo 8, unrotated: a head's output is
-    the histogram of the positions it saw (a block counts as one key with its own histogram), exact in bfloat16 up to
-    the output's rounding.  One key more or fewer moves an entry by a tenth of its size.  Long portions of a bfloat16
-    engine run on the tensor cores, the others and the decoded tokens a warp per row."""
+    """Equal scores (zero queries) and values that are unit vectors by the run of 16 positions a token lies in (modulo
+    8), unrotated: a head's output is the histogram of the runs it saw (a block counts as one key with its own
+    histogram), exact in bfloat16 up to the output's rounding.  One key or block more or fewer moves an entry by
+    1 / (keys seen), far more than that rounding.  Long portions of a bfloat16 engine run on the tensor cores, the
+    others and the decoded tokens a warp per row."""
     from logssms_b200.config.specs import PooledWindowAttentionSpec
     from logssms_b200.parts import PooledWindowAttention
     from logssms_b200.weights.loader import check_and_place
@@ -281,7 +285,8 @@ def test_a_histogram_of_what_was_seen_on_the_tensor_cores_and_off(dtype, window,
     part.bind_tree(check_and_place(part, stored, dtype, "cuda"))
     part.setup(runtime(dtype, max_seq_len=512, page_size=16))
     x = torch.zeros(n, width)
-    x[torch.arange(n), torch.arange(n) % 8] = 1.0
+    mark = lambda j: (j // 16) % 8
+    x[torch.arange(n), (torch.arange(n) // 16) % 8] = 1.0
     pages = 3 * (-(-(max(window, pool) + 140) // 16) + 1)
     for cuts in ([[300]], [[131], [3], [70]] + [[1]] * 96, [[2], [2], [31], [1], [1], [64], [129], [70]]):
         cache, planner = cache_for([part.cache_needs()], dtype, num_pages=pages, max_requests=2, max_seq_len=512)
@@ -290,14 +295,15 @@ def test_a_histogram_of_what_was_seen_on_the_tensor_cores_and_off(dtype, window,
         for i in range(n):
             first, blocks = max(0, i - window + 1), max(0, (i - window + 1) // pool)
             for j in range(first, i + 1):
-                want[i, j % 8] += 1.0
+                want[i, mark(j)] += 1.0
             for b in range(blocks):
                 for j in range(b * pool, (b + 1) * pool):
-                    want[i, j % 8] += 1.0 / pool
+                    want[i, mark(j)] += 1.0 / pool
             want[i] /= (i + 1 - first + blocks)
-        err = (got[:, :8].double() - want).abs().max(-1).values
-        assert float(err.max()) < (1e-5 if dtype == torch.float32 else 2e-3), \
-            f"window {window}, pool {pool}, cuts {cuts[0]}: position {int(err.argmax())} saw something else ({float(err.max()):.3g})"
+        allowed = 1e-5 if dtype == torch.float32 else 0.006 * want + 2e-4        # (bfloat16: the output is rounded twice)
+        err = ((got[:, :8].double() - want).abs() / allowed).max(-1).values
+        assert float(err.max()) <= 1.0, \
+            f"window {window}, pool {pool}, cuts {cuts[0]}: position {int(err.argmax())} saw something else ({float(err.max()):.3g} of what rounding allows)"
 
 
 def test_a_far_block_among_hundreds_still_carries_the_output():
