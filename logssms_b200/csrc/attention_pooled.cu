@@ -472,7 +472,7 @@ extern "C" int lb_pooled_attention_split(const void* q, const void* k_cache, con
 // The keys the run sees - the pooled blocks behind the LAST query's window, then the tokens from the FIRST query's
 // window to the last query - go through shared memory in chunks of kTileK, each row masked per query.  S = Q K^T and
 // P V are `mma.sync` m16n8k16 products of bfloat16 operands with float32 accumulators; scores, maxima, weights and
-// sums are float32.  A weight p enters P V as the two bfloat16 terms hi = bf16(p), lo = bf16(p - hi) (two products
+// sums are float32.  The chunks alternate between two buffers: the next one travels by `cp.async` while this one is used.  A weight p enters P V as the two bfloat16 terms hi = bf16(p), lo = bf16(p - hi) (two products
 // into the same accumulator), so it is applied to 16 bits and more, not rounded to 8.
 constexpr int kTileQ = 64, kTileK = 64, kTileThreads = 128;
 
@@ -507,9 +507,9 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
     const int blocks = max(0, (i_last - window + 1) / pool);        // the blocks the last query sees
     const int keys = blocks + (i_last - first + 1);
     const int k_stride = dim + 8, v_stride = vdim + 8;              // elements; the pad staggers the banks
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(tile_smem);
-    __nv_bfloat16* Vs = Ks + kTileK * k_stride;
-    long* rows_s = reinterpret_cast<long*>(Vs + kTileK * v_stride);  // cache row of every key of the chunk (-1: none)
+    // two buffers of a chunk's keys and values: the next chunk travels (cp.async) while this one is multiplied
+    __nv_bfloat16* Ks0 = reinterpret_cast<__nv_bfloat16*>(tile_smem);
+    __nv_bfloat16* Vs0 = Ks0 + 2 * kTileK * k_stride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
     const int dsteps = dim / 16, vtiles = vdim / 8;
     const int* pages = block_table + (size_t)b * table_width;
@@ -546,35 +546,32 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
 #pragma unroll
     for (int n = 0; n < kValueTiles; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-    for (int k0 = 0; k0 < keys; k0 += kTileK) {
-        __syncthreads();                                             // the chunk before is consumed
-        if (threadIdx.x < kTileK) {
-            const int kk = k0 + threadIdx.x;
-            long row = -1;
-            if (kk < keys) {
-                bool pooled;
-                row = key_row(kk, blocks, first, pages, pooled_pages, page_size, pooled);
-            }
-            rows_s[threadIdx.x] = row;
-        }
-        __syncthreads();
-        {
-            const int kpieces = dim / 8, vpieces = vdim / 8;
-            for (int idx = threadIdx.x; idx < kTileK * (kpieces + vpieces); idx += kTileThreads) {
-                const int r = idx / (kpieces + vpieces), pc = idx % (kpieces + vpieces);
-                const long row = rows_s[r];
-                const bool pooled = (k0 + r) < blocks;
-                uint4 val = make_uint4(0, 0, 0, 0);
-                if (pc < kpieces) {
-                    if (row >= 0) val = *reinterpret_cast<const uint4*>((pooled ? kp_cache : k_cache) + ((size_t)row * Hkv + g) * dim + pc * 8);
-                    *reinterpret_cast<uint4*>(Ks + r * k_stride + pc * 8) = val;
-                } else {
-                    if (row >= 0) val = *reinterpret_cast<const uint4*>((pooled ? vp_cache : v_cache) + ((size_t)row * Hkv + g) * vdim + (pc - kpieces) * 8);
-                    *reinterpret_cast<uint4*>(Vs + r * v_stride + (pc - kpieces) * 8) = val;
-                }
-            }
-        }
-        __syncthreads();
+    // thread 2r copies the key row of the chunk's key r, thread 2r + 1 its value row, in 16-byte pieces; a key that does
+    // not exist (behind the last one, a page that is not there) becomes a row of zeros
+    auto prefetch = [&](int k0, int buf) {
+        const int r = threadIdx.x >> 1;
+        const bool is_v = threadIdx.x & 1;
+        const int kk = k0 + r;
+        long row = -1;
+        bool pooled = false;
+        if (kk < keys) row = key_row(kk, blocks, first, pages, pooled_pages, page_size, pooled);
+        const int n = is_v ? vdim : dim;
+        const __nv_bfloat16* src = is_v ? (pooled ? vp_cache : v_cache) : (pooled ? kp_cache : k_cache);
+        if (row >= 0) src += ((size_t)row * Hkv + g) * n;
+        __nv_bfloat16* dst = is_v ? Vs0 + ((size_t)buf * kTileK + r) * v_stride : Ks0 + ((size_t)buf * kTileK + r) * k_stride;
+        const uint32_t dst_addr = (uint32_t)__cvta_generic_to_shared(dst);
+        const int bytes = row >= 0 ? 16 : 0;
+        for (int pc = 0; pc < n / 8; ++pc)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_addr + pc * 16), "l"(src + (row >= 0 ? pc * 8 : 0)), "r"(bytes));
+        asm volatile("cp.async.commit_group;");
+    };
+    prefetch(0, 0);
+    for (int k0 = 0, it = 0; k0 < keys; k0 += kTileK, ++it) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                             // this chunk has landed; the chunk before is consumed by every warp
+        if (k0 + kTileK < keys) prefetch(k0 + kTileK, (it + 1) & 1);
+        const __nv_bfloat16* Ks = Ks0 + (size_t)(it & 1) * kTileK * k_stride;
+        const __nv_bfloat16* Vs = Vs0 + (size_t)(it & 1) * kTileK * v_stride;
         // is any key of the chunk visible to any row of this warp?
         {
             bool any = false;
@@ -687,7 +684,7 @@ static int launch_tile(const void* q, const void* k_cache, const void* v_cache, 
                        const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* cu,
                        const int* start_pos, const int* tiles, int num_tiles, const float* v_table, int v_rot, int table_rows,
                        void* out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, void* stream) {
-    const size_t smem = (size_t)kTileK * ((dim + 8) + (vdim + 8)) * sizeof(__nv_bfloat16) + kTileK * sizeof(long);
+    const size_t smem = (size_t)2 * kTileK * ((dim + 8) + (vdim + 8)) * sizeof(__nv_bfloat16);
     static size_t have = 0;
     ensure_dynamic_smem(pooled_attention_tile_kernel<kDimSteps, kValueTiles>, smem, have);
     dim3 grid(num_tiles, Hq);
