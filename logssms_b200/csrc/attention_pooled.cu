@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
         int table_width, const int* __restrict__ pooled_table, int pooled_width, const int* __restrict__ cu,
         const int* __restrict__ start_pos, const int* __restrict__ tiles, const float* __restrict__ v_table, int v_rot,
         int table_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale,
-        int window, int pool) {
+        int window, int pool, float* __restrict__ partial, int splits) {
     extern __shared__ __align__(16) unsigned char tile_smem[];
     const int b = tiles[2 * blockIdx.x];
     if (b < 0) return;
@@ -565,11 +565,15 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_addr + pc * 16), "l"(src + (row >= 0 ? pc * 8 : 0)), "r"(bytes));
         asm volatile("cp.async.commit_group;");
     };
-    prefetch(0, 0);
-    for (int k0 = 0, it = 0; k0 < keys; k0 += kTileK, ++it) {
+    // with `splits` > 1 (few tiles: a lone prompt) the CTAs blockIdx.z = 0 .. splits - 1 share the run's chunks; each
+    // leaves its (maximum, sum, weighted values) in `partial`, and `pooled_merge` joins them
+    const int chunks_all = (keys + kTileK - 1) / kTileK, chunks_per = (chunks_all + splits - 1) / splits;
+    const int k_first = min(keys, (int)blockIdx.z * chunks_per * kTileK), k_last = min(keys, k_first + chunks_per * kTileK);
+    if (k_first < k_last) prefetch(k_first, 0);
+    for (int k0 = k_first, it = 0; k0 < k_last; k0 += kTileK, ++it) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                             // this chunk has landed; the chunk before is consumed by every warp
-        if (k0 + kTileK < keys) prefetch(k0 + kTileK, (it + 1) & 1);
+        if (k0 + kTileK < k_last) prefetch(k0 + kTileK, (it + 1) & 1);
         const __nv_bfloat16* Ks = Ks0 + (size_t)(it & 1) * kTileK * k_stride;
         const __nv_bfloat16* Vs = Vs0 + (size_t)(it & 1) * kTileK * v_stride;
         // is any key of the chunk visible to any row of this warp?
@@ -657,6 +661,21 @@ __global__ void __launch_bounds__(kTileThreads) pooled_attention_tile_kernel(
             }
         }
     }
+    if (partial != nullptr) {
+        const int stride = vdim + 2;
+        float* p_lo = partial + (((size_t)(row0 + r_lo) * Hq + head) * splits + blockIdx.z) * stride;
+        float* p_hi = partial + (((size_t)(row0 + r_hi) * Hq + head) * splits + blockIdx.z) * stride;
+        if (tq == 0 && r_lo < n_q) { p_lo[0] = m_lo; p_lo[1] = l_lo; }
+        if (tq == 0 && r_hi < n_q) { p_hi[0] = m_hi; p_hi[1] = l_hi; }
+#pragma unroll
+        for (int n = 0; n < kValueTiles; ++n) {
+            if (n >= vtiles) continue;
+            const int c = n * 8 + 2 * tq;
+            if (r_lo < n_q) { p_lo[2 + c] = o[n][0]; p_lo[3 + c] = o[n][1]; }
+            if (r_hi < n_q) { p_hi[2 + c] = o[n][2]; p_hi[3 + c] = o[n][3]; }
+        }
+        return;
+    }
     // weights' sums, the turn back by the query's position, the store
     const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
     const int half = v_rot >> 1;
@@ -683,33 +702,38 @@ template <int kDimSteps, int kValueTiles>
 static int launch_tile(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache, const void* vp_cache,
                        const int* block_table, int table_width, const int* pooled_table, int pooled_width, const int* cu,
                        const int* start_pos, const int* tiles, int num_tiles, const float* v_table, int v_rot, int table_rows,
-                       void* out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool, void* stream) {
+                       void* out, int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
+                       float* partial, int splits, void* stream) {
     const size_t smem = (size_t)2 * kTileK * ((dim + 8) + (vdim + 8)) * sizeof(__nv_bfloat16);
     static size_t have = 0;
     ensure_dynamic_smem(pooled_attention_tile_kernel<kDimSteps, kValueTiles>, smem, have);
-    dim3 grid(num_tiles, Hq);
+    dim3 grid(num_tiles, Hq, splits);
     pooled_attention_tile_kernel<kDimSteps, kValueTiles><<<grid, kTileThreads, smem, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (const __nv_bfloat16*)kp_cache,
         (const __nv_bfloat16*)vp_cache, block_table, table_width, pooled_table, pooled_width, cu, start_pos, tiles, v_table, v_rot,
-        table_rows, (__nv_bfloat16*)out, Hq, Hkv, dim, vdim, page_size, scale, window, pool);
+        table_rows, (__nv_bfloat16*)out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, splits > 1 ? partial : nullptr, splits);
     return launch_status();
 }
 
 extern "C" int lb_pooled_attention_tile_q() { return kTileQ; }
 
-// bfloat16 only; dim a multiple of 16 up to 128, vdim a multiple of 8 up to 128, an even v_rot
-extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache,
+// bfloat16 only; dim a multiple of 16 up to 128, vdim a multiple of 8 up to 128, an even v_rot.  With `splits` > 1 the chunks of
+// every run are shared by that many CTAs and a merge over ALL `tokens` rows follows (`partial`: float32 scratch of tokens * Hq *
+// splits * (vdim + 2); rows that no run covers hold whatever the scratch held: the caller writes them afterwards).
+static int tile_dispatch(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache,
                                         const void* vp_cache, const int* block_table, int table_width, const int* pooled_table,
                                         int pooled_width, const int* cu, const int* start_pos, const int* tiles, int num_tiles,
                                         const float* v_table, int v_rot, int table_rows, void* out, int Hq, int Hkv, int dim,
-                                        int vdim, int page_size, float scale, int window, int pool, void* stream) {
+                                        int vdim, int page_size, float scale, int window, int pool, float* partial, int splits,
+                                        void* stream) {
     if (num_tiles <= 0) return kOk;
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Hq > 65535 || dim <= 0 || dim % 16 || vdim <= 0 || vdim % 8 || page_size <= 0 || window <= 0
         || pool <= 0 || (v_rot & 1) || v_rot > vdim || table_rows <= 0)
         return kBadSize;
-    if (dim > 128 || vdim > 128) return kTooLarge;
+    if (dim > 128 || vdim > 128 || splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return kTooLarge;
 #define LB_TILE(DS, VT) return launch_tile<DS, VT>(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, pooled_table, \
-        pooled_width, cu, start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, stream)
+        pooled_width, cu, start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale, window, pool, \
+        partial, splits, stream)
     const int ds = dim / 16, vt = vdim / 8;
     if (ds <= 2) { if (vt <= 4) LB_TILE(2, 4); if (vt <= 8) LB_TILE(2, 8); if (vt <= 12) LB_TILE(2, 12); LB_TILE(2, 16); }
     if (ds <= 4) { if (vt <= 4) LB_TILE(4, 4); if (vt <= 8) LB_TILE(4, 8); if (vt <= 12) LB_TILE(4, 12); LB_TILE(4, 16); }
@@ -718,4 +742,20 @@ extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, cons
     if (vt <= 12) LB_TILE(8, 12);
     LB_TILE(8, 16);
 #undef LB_TILE
+}
+
+extern "C" int lb_pooled_attention_tile(const void* q, const void* k_cache, const void* v_cache, const void* kp_cache,
+                                        const void* vp_cache, const int* block_table, int table_width, const int* pooled_table,
+                                        int pooled_width, const int* cu, const int* start_pos, const int* tiles, int num_tiles,
+                                        const int* positions, int tokens, const float* v_table, int v_rot, int table_rows, void* out,
+                                        int Hq, int Hkv, int dim, int vdim, int page_size, float scale, int window, int pool,
+                                        float* partial, int splits, void* stream) {
+    const int code = tile_dispatch(q, k_cache, v_cache, kp_cache, vp_cache, block_table, table_width, pooled_table, pooled_width, cu,
+                                   start_pos, tiles, num_tiles, v_table, v_rot, table_rows, out, Hq, Hkv, dim, vdim, page_size, scale,
+                                   window, pool, partial, splits, stream);
+    if (code != 0 || splits <= 1 || num_tiles <= 0 || tokens <= 0) return code;
+    dim3 grid(tokens, Hq);
+    pooled_merge_kernel<__nv_bfloat16><<<grid, 32, 0, (cudaStream_t)stream>>>(partial, positions, nullptr, v_table, v_rot, table_rows,
+                                                                            (__nv_bfloat16*)out, Hq, vdim, splits);
+    return launch_status();
 }

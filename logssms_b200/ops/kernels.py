@@ -1633,24 +1633,37 @@ def pooled_attention_tile_ok(q: torch.Tensor, v_cache: torch.Tensor) -> bool:
     return POOLED_TILE and q.dtype == torch.bfloat16 and dim % 16 == 0 and dim <= 128 and vdim % 8 == 0 and vdim <= 128
 
 
+def pooled_tile_splits(num_tiles: int, num_heads: int) -> int:
+    """CTAs that share a run's chunks of keys in the tensor-core form: 1 where the runs fill the GPU twice by themselves,
+    up to 4 for a lone prompt."""
+    return max(1, min(4, -(-2 * _SM_COUNT // max(num_tiles * num_heads, 1))))
+
+
 def pooled_attention_tile(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kp_cache: torch.Tensor, vp_cache: torch.Tensor,
                           block_table: torch.Tensor, pooled_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor,
-                          tiles: torch.Tensor, v_table: torch.Tensor, scale: float, window: int, pool: int, out: torch.Tensor) -> torch.Tensor:
+                          positions: torch.Tensor, tiles: torch.Tensor, v_table: torch.Tensor, scale: float, window: int, pool: int,
+                          out: torch.Tensor, splits: int = 1) -> torch.Tensor:
     """The same attention for the long portions' runs of `pooled_attention_tile_q()` tokens (work list of
-    `StepContext.long_portion_tiles`) on the tensor cores; writes those tokens' rows of `out` [tokens, heads * value_dim]."""
-    _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, cu_seqlens, start_pos, tiles, v_table, out)
-    for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (tiles, "tiles")):
+    `StepContext.long_portion_tiles`) on the tensor cores; writes those tokens' rows of `out` [tokens, heads * value_dim].
+    With `splits` > 1 that many CTAs share a run's keys and a merge follows, which also writes the rows that no run covers
+    (with nothing of meaning: the caller fills them afterwards)."""
+    _cuda(q, k_cache, v_cache, kp_cache, vp_cache, block_table, pooled_table, cu_seqlens, start_pos, positions, tiles, v_table, out)
+    for t, name in ((block_table, "block_table"), (pooled_table, "pooled_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"),
+                    (tiles, "tiles"), (positions, "positions")):
         _i32(t, name)
     T, H, dim = q.shape
     G, vdim = v_cache.shape[2], v_cache.shape[3]
     _need(q.is_contiguous() and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
           and out.is_contiguous() and out.shape == (T, H * vdim), "the tensor-core form takes contiguous bfloat16 tensors")
+    partial = torch.empty((T, H, splits, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     f = _fn("attention_pooled", "lb_pooled_attention_tile", [c_void_p] * 6 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                             c_void_p, c_int, c_int, c_void_p] + [c_int] * 5 + [c_float, c_int, c_int, c_void_p])
+                                                             c_void_p, c_int, c_void_p, c_int, c_int, c_void_p] + [c_int] * 5
+            + [c_float, c_int, c_int, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kp_cache), _ptr(vp_cache), _ptr(block_table), block_table.shape[1],
-             _ptr(pooled_table), pooled_table.shape[1], _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(v_table),
-             v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool, _stream()),
-           "pooled_attention_tile", f"(dim {dim}, value dim {vdim})")
+             _ptr(pooled_table), pooled_table.shape[1], _ptr(cu_seqlens), _ptr(start_pos), _ptr(tiles), tiles.shape[0], _ptr(positions), T,
+             _ptr(v_table), v_table.shape[1], max(v_table.shape[0], 1), _ptr(out), H, G, dim, vdim, k_cache.shape[1], scale, window, pool,
+             _ptr(partial), splits, _stream()),
+           "pooled_attention_tile", f"(dim {dim}, value dim {vdim})", launches=2 if splits > 1 else 1)
     return out
 
 

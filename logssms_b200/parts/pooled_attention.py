@@ -101,11 +101,12 @@ class PooledWindowAttention(Part):
         if ctx.has_long_portions and K.pooled_attention_tile_ok(q, v_cache):
             # long portions on the tensor cores: runs of neighbouring tokens share their keys through shared memory; decoded
             # tokens and short portions (other rows of the output) a warp per (token, head)
-            tiles, _ = ctx.long_portion_tiles(K.pooled_attention_tile_q())
+            tiles, n_tiles = ctx.long_portion_tiles(K.pooled_attention_tile_q())
             short, n_short = ctx.short_portion_tokens()
             o = torch.empty((x.shape[0], s.num_heads * s.value_dim), dtype=q.dtype, device=q.device)
-            K.pooled_attention_tile(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.cu_seqlens, ctx.start_pos, tiles,
-                                    self.value_position.table, s.softmax_scale, s.window, s.pool, o)
+            K.pooled_attention_tile(q, k_cache, v_cache, kp_cache, vp_cache, *tables, ctx.cu_seqlens, ctx.start_pos, ctx.positions,
+                                    tiles, self.value_position.table, s.softmax_scale, s.window, s.pool, o,
+                                    splits=K.pooled_tile_splits(n_tiles, s.num_heads))
             if n_short > 0:
                 few_rows(short, o, n_short)
         else:
