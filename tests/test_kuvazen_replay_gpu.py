@@ -77,7 +77,7 @@ def replayed(tmp_path_factory, name, dtype):
 
 @pytest.mark.parametrize("scenario", SCENARIOS)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "R3", "R9", "R12"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "R3", "R9", "R12"])
 def test_replay_matches_plain(tmp_path_factory, name, dtype, scenario):
     got, want, ids_of, floor = replayed(tmp_path_factory, name, dtype)
     checked = 0

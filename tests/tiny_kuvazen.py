@@ -77,6 +77,15 @@ KUVA_E = _model(48, 77, 1e-5, 4, (0, 1, 2), [
 ])
 
 
+# F: nothing is a multiple of 8, or even of 2 where the design allows it: an odd width and vocabulary, a recurrent width,
+# feed-forward sizes and a side input that are odd, head sizes of 12 and 20 (no 16-byte rows anywhere)
+KUVA_F = _model(45, 101, 1e-5, 5, (1, 3, 2), [
+    {**_attn(3, 1, 12, 20, 6, 11, 3), "mlp": _dense(31, 1.0)},
+    {**_gru(33), "mlp": _moe(19, 3, 2)},
+    {**_attn(2, 2, 6, 10, 6, 30, 7, base=777.0), "mlp": None},
+])
+
+
 def random_kuvazen(seed: int) -> dict:
     """A configuration with every size and option drawn at random within what config.json allows."""
     import random
@@ -105,7 +114,7 @@ def random_kuvazen(seed: int) -> dict:
                   rng.choice([None, (a, b, rng.randint(1, 3))]), layers)
 
 
-KUVA = {"A": KUVA_A, "B": KUVA_B, "C": KUVA_C, "D": KUVA_D, "E": KUVA_E}
+KUVA = {"A": KUVA_A, "B": KUVA_B, "C": KUVA_C, "D": KUVA_D, "E": KUVA_E, "F": KUVA_F}
 KUVA.update({f"R{seed}": random_kuvazen(seed) for seed in range(1, 13)})
 
 
